@@ -1,0 +1,131 @@
+// Row-wise and element-wise kernels: embedding gather, residual add + RMSNorm, SwiGLU, casts.
+//
+// The residual stream is float32 in every mode; sums of squares, the residual sum and the activation are
+// computed in float32 in a fixed order that depends on the row width only, so a row's result does not
+// depend on how many rows the launch has.
+//
+// Formulas (reference): RMSNorm y = x * rsqrt(mean(x^2) + eps) * w with the add fused in front
+// (src/gpu_ops.hip:24-56, 64-101); SwiGLU out = g / (1 + exp(-g)) * u (src/gpu_ops.hip:103-114);
+// embedding x[t] = table[token[t]] without scaling (src/qwen_model.cpp:1234-1244).
+#include "common.cuh"
+
+namespace {
+
+using namespace ph;
+
+template <typename TT>
+__global__ void embed_gather_kernel(const TT* __restrict__ table, const int32_t* __restrict__ ids,
+                                    float* __restrict__ out, int E, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);       // ids are validated on the host; never read outside
+    const TT* row = table + (size_t)id * E;
+    float* o = out + (size_t)t * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) o[i] = to_float<TT>(row[i]);
+}
+
+// One block per output row.  v = x[t] + sum_s add[s][t]; optionally stored back to x; y = rmsnorm(v) * w.
+template <typename TA, typename TY, int NT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
+                                   long long add_split_stride, const float* __restrict__ weight, float eps,
+                                   const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
+    extern __shared__ float row_buf[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float* xr = x + (size_t)t * E;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < E; i += NT) {
+        float v = xr[i];
+        if (add) {
+            const TA* a = add + (size_t)t * E + i;
+            for (int s = 0; s < add_splits; ++s) v += to_float<TA>(a[(size_t)s * add_split_stride]);
+            if (write_x) xr[i] = v;
+        }
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    if (!weight) return;
+    const float total = block_sum<NT>(ss, scratch);
+    const float inv = rsqrtf(total / (float)E + eps);
+    TY* yr = y + (size_t)r * E;
+    for (int i = threadIdx.x; i < E; i += NT) yr[i] = from_float<TY>(row_buf[i] * inv * weight[i]);
+}
+
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
+                              int FF, long long total) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long t = idx / FF;
+    const int j = (int)(idx - t * FF);
+    const TI* g = gu + t * 2 * FF + j;
+    float gv = 0.0f, uv = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        gv += to_float<TI>(g[(size_t)s * split_stride]);
+        uv += to_float<TI>(g[(size_t)s * split_stride + FF]);
+    }
+    out[idx] = from_float<TO>(gv / (1.0f + expf(-gv)) * uv);
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(to_float<TI>(in[i]));
+}
+
+}  // namespace
+
+PH_EXPORT int ph_embed_gather(const void* table, int table_dtype, const int32_t* ids, float* out, int T, int E, int V,
+                              cudaStream_t stream) {
+    if (!table || !ids || !out || T < 0 || E < 1 || V < 1 || !valid_dtype(table_dtype))
+        return fail(PH_ERR_ARG, "embed_gather: bad arguments (T %d, E %d, V %d, dtype %d)", T, E, V, table_dtype);
+    if (T == 0) return PH_OK;
+    PH_DISPATCH(table_dtype, TT, embed_gather_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, out, E, V));
+    return check_launch("embed_gather");
+}
+
+PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_splits, long long add_split_stride,
+                             const float* weight, float eps, const int32_t* rows, int n_out, int E, void* y,
+                             int y_dtype, int write_x, cudaStream_t stream) {
+    if (!x || n_out < 0 || E < 1 || !valid_dtype(add_dtype) || !valid_dtype(y_dtype) || (weight && !y) ||
+        (add && add_splits < 1))
+        return fail(PH_ERR_ARG, "add_rmsnorm: bad arguments (rows %d, E %d)", n_out, E);
+    if (rows && write_x && add) return fail(PH_ERR_ARG, "add_rmsnorm: a gathered launch cannot write x back");
+    if (n_out == 0) return PH_OK;
+    const size_t smem = (size_t)E * sizeof(float);
+    if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "add_rmsnorm: width %d exceeds the supported 51200", E);
+    constexpr int NT = 256;
+#define LAUNCH(TA, TY)                                                                                          \
+    do {                                                                                                        \
+        auto k = add_rmsnorm_kernel<TA, TY, NT>;                                                                \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        k<<<n_out, NT, smem, stream>>>(x, (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E,   \
+                                       (TY*)y, write_x);                                                        \
+    } while (0)
+    PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, LAUNCH(TA, TY)));
+#undef LAUNCH
+    return check_launch("add_rmsnorm");
+}
+
+PH_EXPORT int ph_swiglu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out,
+                        int out_dtype, int T, int FF, cudaStream_t stream) {
+    if (!gate_up || !out || T < 0 || FF < 1 || splits < 1 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "swiglu: bad arguments (T %d, FF %d)", T, FF);
+    const long long total = (long long)T * FF;
+    if (total == 0) return PH_OK;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+        swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)gate_up, splits, split_stride, (TO*)out, FF, total)));
+    return check_launch("swiglu");
+}
+
+PH_EXPORT int ph_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (!in || !out || n < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "cast: bad arguments");
+    if (n == 0) return PH_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+        cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, n)));
+    return check_launch("cast");
+}

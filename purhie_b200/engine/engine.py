@@ -1,0 +1,235 @@
+"""The engine: a model, its cache and the one step function.
+
+``Engine.step(entries)`` takes a batch of (request, its next tokens, the places whose logits are wanted):
+portions of prompts beside single decoded tokens, cut anywhere.  It runs only the tokens it is given, as
+one batch, against the cache that earlier steps left, and returns float32 logits at the wanted places.
+The scheduler, the Python entry point and the trace replay tool all drive this function; there is no
+other forward pass.  The reference has three entry points instead (one decode row, consecutive rows of
+one sequence, one decode row of each of n sequences: src/qwen_model.h:36-42, 150-161) and never mixes
+prompt portions with decode rows in one pass (src/inference.cpp:3071-3143).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages, OutOfSlots
+from ..config.base import ModelConfig, load_config, lookup_architecture
+from ..parts.context import GroupStep, StepContext, Workspace
+from ..parts.model import DecoderModel
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    """A batch that cannot be run: an unknown token id, a position past the model's limit, a request in
+    the batch twice."""
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()             # places among ``tokens`` whose logits are returned
+
+
+@dataclass
+class StepStats:
+    tokens: int = 0
+    prompt_rows: int = 0
+    decode_rows: int = 0
+    wanted: int = 0
+    pages_free: List[int] = field(default_factory=list)
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {dtype} is not supported (bfloat16 or float32)")
+        return dtype
+    try:
+        return _DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not supported (bfloat16 or float32)") from None
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, config: Optional[ModelConfig], *, page_size: int = 16,
+                 max_tokens: int = 4096, max_requests: int = 4, num_pages=None, device="cuda:0",
+                 poison_cache: bool = False):
+        """``model`` is bound to its weights already.  The cache holds ``max_tokens`` tokens per page group
+        (each request's count rounded up to whole pages) for up to ``max_requests`` live requests;
+        ``num_pages`` overrides the page count (one number or one per group)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("purhie_b200 runs on a CUDA device only; no GPU is visible and there is no host path")
+        self.model = model
+        self.config = config
+        self.device = torch.device(device)
+        self.dtype = model.compute_dtype
+        self.page_size = page_size
+        self.max_requests = max_requests
+        if num_pages is None:
+            num_pages = -(-max_tokens // page_size)
+        self.cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests)
+        self.cache.materialize(self.device, self.dtype, poison=poison_cache)
+        self.views = model.cache_views(self.cache)
+        self.workspace = Workspace(self.device)
+        self.vocab_size = model.spec.vocab_size
+        self.max_position = model.spec.max_position
+        self.last_stats = StepStats()
+        self._meta_host = [(None, None), (None, None)]
+        self._meta_turn = 0
+        from ..csrc.build import load_library
+        for lib in model.required_libraries():          # compile what this model needs, now
+            load_library(lib)
+
+    # ---- construction ----------------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0", options: Optional[dict] = None,
+                    **kw) -> "Engine":
+        arch, config = load_config(model_dir)
+        model = DecoderModel(arch.build_spec(config), parse_dtype(dtype), options)
+        model.load(model_dir, device)
+        return cls(model, config, device=device, **kw)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02,
+                    scale_low: float = 1.0, scale_high: float = 1.0, options: Optional[dict] = None,
+                    **kw) -> "Engine":
+        """Random weights made directly on the device (no folder is written).  Values differ from those of
+        :func:`purhie_b200.weights.write_random_model`, which draws on the host."""
+        from ..weights.loader import device_dtype
+        from ..weights.random_init import random_tensor
+        dt = parse_dtype(dtype)
+        arch = lookup_architecture(config.architecture)
+        model = DecoderModel(arch.build_spec(config), dt, options)
+        tensors = {}
+        for name, spec in model.tensor_specs().items():
+            t = random_tensor(spec, seed, std, scale_low, scale_high, device=device)
+            tensors[name] = t.to(device_dtype(torch.bfloat16, spec.role, dt))
+        model.bind(tensors, device)
+        return cls(model, config, device=device, **kw)
+
+    # ---- requests --------------------------------------------------------------------------------
+    def add_request(self, request_id) -> None:
+        self.cache.add_request(request_id)
+
+    def has_request(self, request_id) -> bool:
+        return self.cache.has_request(request_id)
+
+    def release(self, request_id) -> None:
+        self.cache.release(request_id)
+
+    def length(self, request_id) -> int:
+        return self.cache.length(request_id)
+
+    # ---- the step --------------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} is in the batch twice")
+            seen.add(e.request_id)
+            if not self.cache.has_request(e.request_id):
+                raise StepError(f"request {e.request_id!r} is not live (add_request first)")
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary of "
+                                    f"{self.vocab_size}")
+            if self.cache.length(e.request_id) + n > self.max_position:
+                raise StepError(f"request {e.request_id!r} would reach position "
+                                f"{self.cache.length(e.request_id) + n}, the model's limit is {self.max_position}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
+
+    def build_context(self, entries: Sequence[StepEntry], table_width: Optional[int] = None):
+        """Reserve pages and upload the batch's metadata.  Returns (ctx, want_rows, n_want)."""
+        cache, ps = self.cache, self.page_size
+        reserved = []
+        try:
+            for e in entries:
+                cache.reserve(e.request_id, len(e.tokens))
+                reserved.append(e)
+        except OutOfPages:
+            # give back what this step took, so that a refused step changes nothing
+            for e in reserved:
+                cache.unreserve(e.request_id)
+            raise
+        tokens, positions, row_seg, seg_start, ctx_lens, q_lens, slots, want = [], [], [], [0], [], [], [], []
+        for s, e in enumerate(entries):
+            start = cache.length(e.request_id)
+            n = len(e.tokens)
+            base = len(tokens)
+            tokens.extend(int(t) for t in e.tokens)
+            positions.extend(range(start, start + n))
+            row_seg.extend([s] * n)
+            seg_start.append(base + n)
+            ctx_lens.append(start + n)
+            q_lens.append(n)
+            slots.append(cache.slot_of(e.request_id))
+            want.extend(base + int(w) for w in e.want)
+        T, S, G = len(tokens), len(entries), len(cache.groups)
+        widths = []
+        for g in cache.groups:
+            w = max(len(cache.block_table(e.request_id, g.index)) for e in entries)
+            widths.append(max(table_width or 0, -(-w // 8) * 8))
+        # one packed int32 buffer, one copy
+        sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * G
+        total = sum(sizes)
+        # two pinned buffers in turn: a buffer is rewritten only after the copy that last read it is done
+        self._meta_turn ^= 1
+        buf, event = self._meta_host[self._meta_turn]
+        if buf is None or buf.numel() < total:
+            buf = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
+            event = torch.cuda.Event()
+        else:
+            event.synchronize()
+        self._meta_host[self._meta_turn] = (buf, event)
+        host = buf[:total]
+        flat: List[int] = []
+        flat += tokens + positions + row_seg + seg_start + ctx_lens + slots + (want if want else [0])
+        for g, w in zip(cache.groups, widths):
+            for e in entries:
+                table = cache.block_table(e.request_id, g.index)
+                flat += table + [-1] * (w - len(table))
+        for g in cache.groups:
+            for e in entries:
+                flat += cache.token_slots(e.request_id, g.index, cache.length(e.request_id), len(e.tokens))
+        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        dev = self.workspace.get("step_meta", (total,), torch.int32)
+        dev.copy_(host, non_blocking=True)
+        event.record()
+        parts, off = [], 0
+        for n in sizes:
+            parts.append(dev[off:off + n])
+            off += n
+        groups = [GroupStep(parts[7 + i].view(S, widths[i]), parts[7 + G + i], ps) for i in range(G)]
+        ctx = StepContext(T=T, S=S, token_ids=parts[0], positions=parts[1], row_seg=parts[2], seg_start=parts[3],
+                          seg_ctx_len=parts[4], seg_slot=parts[5], q_lens=q_lens, ctx_lens=ctx_lens, groups=groups,
+                          workspace=self.workspace, compute_dtype=self.dtype,
+                          decode_only=all(q == 1 for q in q_lens))
+        return ctx, parts[6], len(want)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits [wanted places, vocab] on the device in the order of the
+        entries and of each entry's ``want`` (None when nothing is wanted).  Raises :class:`OutOfPages`,
+        leaving everything as it was, when the cache cannot hold the batch."""
+        entries = list(entries)
+        if not entries:
+            return None
+        self._validate(entries)
+        ctx, want_rows, n_want = self.build_context(entries)
+        logits = self.model.forward(ctx, self.views, want_rows, n_want)
+        for e in entries:
+            self.cache.advance(e.request_id, len(e.tokens))
+        self.last_stats = StepStats(tokens=ctx.T, prompt_rows=sum(q for q in ctx.q_lens if q > 1),
+                                    decode_rows=sum(1 for q in ctx.q_lens if q == 1), wanted=n_want,
+                                    pages_free=self.cache.free_pages())
+        return logits
