@@ -233,3 +233,37 @@ class Engine:
                                     decode_rows=sum(1 for q in ctx.q_lens if q == 1), wanted=n_want,
                                     pages_free=self.cache.free_pages())
         return logits
+
+    # ---- sampling --------------------------------------------------------------------------------
+    def sample(self, logits: torch.Tensor, samplers) -> List[int]:
+        """One token per row of ``logits`` with the row's sampler.  Greedy and plain temperature sampling run
+        in the device kernels (the uniform number still comes from the sampler's generator, one per token);
+        every other chain runs on the host over a copy of the row."""
+        from ..csrc import ops
+        R = len(samplers)
+        if logits is None or logits.shape[0] != R:
+            raise StepError(f"{R} samplers for {0 if logits is None else logits.shape[0]} rows of logits")
+        modes = [s.device_mode() for s in samplers]
+        out: List[Optional[int]] = [None] * R
+        if "greedy" in modes:
+            ids = self.workspace.get("sample_greedy", (R,), torch.int32)
+            ops.argmax(logits, ids)
+            host = ids.cpu().tolist()
+            for i, m in enumerate(modes):
+                if m == "greedy":
+                    out[i] = host[i]
+        if "temperature" in modes:
+            temps = torch.tensor([s.params.temperature if m == "temperature" else 1.0
+                                  for s, m in zip(samplers, modes)], dtype=torch.float32)
+            unis = torch.tensor([s.uniform() if m == "temperature" else 0.0 for s, m in zip(samplers, modes)],
+                                dtype=torch.float64)
+            ids = self.workspace.get("sample_temp", (R,), torch.int32)
+            ops.sample_temperature(logits, temps.to(self.device), unis.to(self.device), ids)
+            host = ids.cpu().tolist()
+            for i, m in enumerate(modes):
+                if m == "temperature":
+                    out[i] = host[i]
+        for i, m in enumerate(modes):
+            if m is None:
+                out[i] = samplers[i].sample(logits[i].float().cpu().numpy())
+        return out

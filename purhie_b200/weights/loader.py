@@ -98,7 +98,10 @@ def load_tensors(model_dir: str, expected: Dict[str, TensorSpec], compute_dtype:
         for name, spec in expected.items():
             src = folder.tensor(name)
             dt = device_dtype(src.dtype, spec.role, compute_dtype)
-            out[name] = src.to(device=device).to(dtype=dt).contiguous()
+            t = src.to(device=device).to(dtype=dt).contiguous()
+            if t.data_ptr() == src.data_ptr():
+                t = t.clone()                       # never hand out a view of the file mapping
+            out[name] = t
         return out
     finally:
         folder.close()

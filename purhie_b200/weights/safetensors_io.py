@@ -102,12 +102,7 @@ class SafetensorsFile:
         return t.view(entry.shape)
 
     def close(self) -> None:
-        # Views made by tensor() keep the mapping alive; closing is left to the garbage collector when
-        # such views exist.
-        try:
-            self._map.close()
-        except BufferError:
-            pass
+        # The mapping itself is left to the garbage collector: tensors made by tensor() point into it.
         self._f.close()
 
 

@@ -1,0 +1,135 @@
+"""The plain implementation and the host sampler against the reference's own CPU code (no GPU).
+
+tests/golden/ref_ops.json holds what the reference's src/qwen_ops.cpp and src/sampler.cpp compute on fixed
+inputs (made by tests/golden/make_golden.py).
+"""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+from purhie_b200.sampling import MT19937_64, Sampler, SamplerParams
+from helpers import TINY_A, TINY_A_INIT, TINY_B, TINY_B_INIT, make_model, random_tokens
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "ref_ops.json")))
+
+
+def t64(name):
+    return torch.tensor(GOLD[name], dtype=torch.float64)
+
+
+def test_rmsnorm_matches_the_reference():
+    y = P.rmsnorm(t64("rms_x"), t64("rms_w"), 1e-5)
+    assert (y - t64("rms_y")).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("pos", [0, 7, 1234])
+def test_rope_matches_the_reference(pos):
+    v = t64("rope_in").view(1, 1, 32)
+    full = P.rope_rotate_half(v, [pos], 1e6, 32).view(-1)
+    half = P.rope_rotate_half(v, [pos], 10000.0, 16).view(-1)
+    assert (full - t64(f"rope_full_theta1e6_pos{pos}")).abs().max() < 1e-6
+    assert (half - t64(f"rope_half_theta1e4_pos{pos}")).abs().max() < 1e-6
+    assert torch.equal(half[16:], v.view(-1)[16:])           # dims >= n_rot pass through
+
+
+def test_attention_matches_the_reference():
+    H, HKV, D, N = 8, 2, 32, 37
+    q = t64("attn_q").view(1, H, D)
+    k, v = t64("attn_k").view(N, HKV, D), t64("attn_v").view(N, HKV, D)
+    # the reference attends one query over N cached positions: the last row of a causal pass over N rows
+    qq = torch.zeros(N, H, D, dtype=torch.float64)
+    qq[-1] = q[0]
+    out = P.attention(qq, k, v, 0.17677669529663687)[-1].reshape(-1)
+    assert (out - t64("attn_out")).abs().max() < 1e-5
+
+
+def test_silu_matches_the_reference():
+    x = t64("silu_x")
+    assert (x / (1 + torch.exp(-x)) - t64("silu_y")).abs().max() < 1e-6
+
+
+def test_window_masks_exactly_the_positions_before_it():
+    torch.manual_seed(0)
+    T, W = 12, 5
+    q, k, v = (torch.randn(T, 2, 8, dtype=torch.float64) for _ in range(3))
+    full, win = P.attention(q, k, v, 0.3), P.attention(q, k, v, 0.3, window=W)
+    assert torch.allclose(full[:W], win[:W])                # the first W positions see everything
+    z = T - 1
+    manual = P.attention(q[z - W + 1:], k[z - W + 1:], v[z - W + 1:], 0.3)[-1]
+    assert torch.allclose(win[z], manual)                   # a token at z sees positions > z - W only
+
+
+def test_forward_is_causal_and_uses_the_tied_head(tmp_path):
+    make_model(tmp_path, TINY_A, TINY_A_INIT)
+    cfg, w = P.read_model(str(tmp_path))
+    toks = random_tokens(20, 256, 1)
+    full = P.forward(cfg, w, toks)
+    assert full.shape == (20, 256)
+    assert torch.allclose(P.forward(cfg, w, toks[:9]), full[:9], atol=1e-12)
+    assert "lm_head.weight" not in w
+
+
+def test_layer_windows_from_config_keys():
+    assert P.layer_windows(TINY_B) == [None, 24, 24]
+    assert P.layer_windows(TINY_A) == [None, None]
+    assert P.layer_windows(dict(TINY_A, layer_types=["sliding_attention", "full_attention"], sliding_window=7)) == [7, None]
+
+
+# ---- sampler -------------------------------------------------------------------------------------------
+
+def test_mt19937_64_is_the_standard_generator():
+    g = MT19937_64(5489)
+    for _ in range(9999):
+        g.next_u64()
+    assert g.next_u64() == 9981545732273789042              # the C++ standard's check value
+
+
+def test_greedy_lowest_id_wins_ties():
+    l = np.array(GOLD["samp_logits"], dtype=np.float32)
+    assert Sampler(SamplerParams.greedy()).sample(l) == GOLD["samp_greedy"] == 11
+    assert P.greedy(l) == 11
+
+
+@pytest.mark.parametrize("name,params", [
+    ("samp_default_seed3", SamplerParams(seed=3)),
+    ("samp_temp_only_seed1", SamplerParams(temperature=0.7, top_k=0, top_p=1.0, min_p=0.0, seed=1)),
+    ("samp_topp_only_seed5", SamplerParams(temperature=1.3, top_k=0, top_p=0.6, min_p=0.0, seed=5)),
+    ("samp_penalty_seed9", SamplerParams(temperature=1.0, top_k=10, top_p=1.0, min_p=0.0, repeat_penalty=1.3,
+                                         presence_penalty=0.5, seed=9)),
+])
+def test_sampler_chain_draws_the_reference_tokens(name, params):
+    l = np.array(GOLD["samp_logits"], dtype=np.float32)
+    s = Sampler(params)
+    got = []
+    for _ in range(40):
+        t = s.sample(l)
+        s.accept(t)
+        got.append(t)
+    assert got == GOLD[name]
+
+
+def test_temperature_distribution():
+    l = np.array(GOLD["samp_logits"], dtype=np.float32)
+    p = P.temperature_probabilities(l, 0.7)
+    s = Sampler(SamplerParams.pure_temperature(0.7, seed=2))
+    counts = np.zeros_like(p)
+    n = 20000
+    for _ in range(n):
+        counts[s.sample(l)] += 1
+    assert np.abs(counts / n - p).max() < 0.012
+    assert s.device_mode() == "temperature" and Sampler(SamplerParams()).device_mode() is None
+    assert Sampler(SamplerParams.greedy()).device_mode() == "greedy"
+
+
+def test_reset_reseeds_and_forgets():
+    l = np.array(GOLD["samp_logits"], dtype=np.float32)
+    s = Sampler(SamplerParams(seed=4, repeat_penalty=1.2))
+    a = [s.sample(l) for _ in range(5)]
+    s.accept(3)
+    s.reset()
+    assert [s.sample(l) for _ in range(5)] == a and not s.history
