@@ -1,6 +1,100 @@
-"""Python face of the tcgen05 matrix product (gemm_tcgen05.cu)."""
+"""Python face of the tcgen05 matrix product (gemm_tcgen05.cu) and the choice of its shape.
+
+Few tokens (decoding, short portions): the weight fills the 128-row side of the tensor-core instruction
+and the tokens the other side ("swapped"), K is split over CTAs so that all SMs stream weights, and the
+float32 partial results are summed by the kernel that consumes the product.  Many tokens: 128-token by
+256-feature tiles.
+"""
 from __future__ import annotations
 
+from ctypes import c_int, c_void_p
+from typing import Optional
 
-def supports(weight) -> bool:
-    return False
+import torch
+
+from . import ops
+from .ops import KernelError, call, register_signatures
+
+register_signatures("gemm100", {
+    "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p, c_void_p],
+})
+
+BLOCK_K = 64
+_flags = {}
+_sm_count = {}
+
+ERRORS = {101: "the TMA producer waited too long for a free stage", 102: "the MMA warp waited too long",
+          103: "the epilogue waited too long for an accumulator"}
+
+
+def supports(weight: torch.Tensor) -> bool:
+    return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0
+            and weight.data_ptr() % 16 == 0 and weight.is_contiguous())
+
+
+def error_flag(device) -> torch.Tensor:
+    key = torch.device(device)
+    if key not in _flags:
+        _flags[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _flags[key]
+
+
+def check_errors(device) -> None:
+    """Raise if a kernel gave up on a wait since the last check (synchronises the device)."""
+    key = torch.device(device)
+    if key in _flags:
+        code = int(_flags[key].item())
+        if code:
+            _flags[key].zero_()
+            raise KernelError(f"gemm_tcgen05: {ERRORS.get(code, 'error')} (status {code})")
+
+
+def sm_count(device) -> int:
+    key = torch.device(device)
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_count[key]
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, block_n: int, splits: int = 1,
+         max_ctas: int = 0) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1)."""
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise KernelError(f"gemm_tcgen05: {name} must be a contiguous bfloat16 CUDA tensor")
+    N, K = w.shape
+    M = x.numel() // K
+    if x.shape[-1] != K or out.numel() != splits * M * N or not out.is_contiguous():
+        raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    call("gemm100", "ph_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
+         1 if swapped else 0, block_n, splits, max_ctas, error_flag(x.device).data_ptr(), ops._stream())
+    return out
+
+
+def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
+    """(swapped, block_n, splits) for a product of M tokens with an [N, K] weight."""
+    kblocks = -(-K // BLOCK_K)
+    if M >= 128:
+        return False, (256 if N > 128 else 128 if N > 64 else 64), 1
+    block_n = 16
+    while block_n < M:
+        block_n *= 2
+    splits = 1
+    if allow_split:
+        a_tiles = -(-N // 128)
+        if a_tiles < sms:
+            splits = max(1, min(sms // a_tiles, kblocks // 4))
+    return True, block_n, splits
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool):
+    from ..parts.base import Addend
+    N, K = w.shape
+    swapped, block_n, splits = plan(M, N, K, sm_count(x.device), allow_split)
+    if splits > 1:
+        out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)
+    else:
+        out = ctx.workspace.get(out_name, (M, N), out_dtype)
+    gemm(x[:M], w, out, swapped=swapped, block_n=block_n, splits=splits)
+    return Addend(out, splits)

@@ -1,0 +1,452 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: D[a, b] = sum_k A[a, k] * B[b, k], both
+// operands K-major in global memory, float32 accumulation in tensor memory (TMEM).
+//
+// One persistent CTA per SM walks over work items (tile of 128 A-rows x BN B-rows, split of K).  Warp 0 is
+// the TMA producer (one elected lane): it copies 128 x 64 and BN x 64 element boxes, 128-byte swizzled, into
+// a ring of shared-memory stages and signals a "full" mbarrier per stage.  Warp 1 allocates TMEM and issues
+// tcgen05.mma (M = 128, N = BN, K = 16 per instruction) from one lane, releasing a stage with
+// tcgen05.commit.  Warps 2-5 are the epilogue: they read the accumulator with tcgen05.ld (each warp its own
+// 32-lane quarter), convert and store it, while the MMA warp already fills the second accumulator buffer.
+//
+// Two orientations share the kernel.  Plain: A = activations [tokens, K], B = weight [features, K], the
+// thread that holds accumulator row a writes out[a, b0 .. b0+BN).  Swapped (few tokens: decoding): A =
+// weight, B = activations, so that the 128-row side of the instruction is filled by output features and the
+// few tokens sit on the N side; the accumulator is stored transposed, out[b, a].  With splits > 1 each
+// split of K writes its own float32 partial result [split][tokens][features]; whoever consumes the product
+// adds the partials in order (the norm, rotary and activation kernels take them), which keeps the sum
+// deterministic.
+//
+// No cluster multicast is used: every CTA fetches its own tiles.  Every wait on an mbarrier is bounded; a
+// wait that runs out sets *error_flag, and the CTA still frees its TMEM and returns.
+// The reference's counterpart is its WMMA tile kernel for gfx1151 (src/matvec_q.hip:3437-3547).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+using namespace ph;
+
+constexpr int BM = 128;          // rows of the A tile = M of the instruction
+constexpr int BK = 64;           // K elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+#define PH_ERR_WAIT_PRODUCER 101
+#define PH_ERR_WAIT_MMA 102
+#define PH_ERR_WAIT_EPILOGUE 103
+
+struct GemmParams {
+    int rows_a, rows_b, K;
+    int a_tiles, b_tiles, splits, kblocks;
+    void* out;
+    int out_bf16;        // 1: bfloat16 output, 0: float32
+    int swapped;
+    long long ld;        // row length of out
+    long long split_stride;
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (after setting the error flag) when the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* error_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && global_timer() - t0 > WAIT_LIMIT_NS) {
+            atomicExch(error_flag, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c_inner, int c_row) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c_inner), "r"(c_row) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of 8
+// rows 1024 bytes apart.  Bits: [0,14) address >> 4, [16,30) leading byte offset >> 4 (unused with this
+// swizzle), [32,46) stride byte offset >> 4, [46,48) version 1, [61,64) swizzle mode 2 (128 bytes).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both
+// K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct TileConfig {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 10 ? 10 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : 2 * BN;          // a power of two: BN is one
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    using Cfg = TileConfig<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int work_total = p.a_tiles * p.b_tiles * p.splits;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
+                const int split = w % p.splits, tile = w / p.splits;
+                const int a0 = (tile % p.a_tiles) * BM, b0 = (tile / p.a_tiles) * BN;
+                const int kb0 = (int)((long long)p.kblocks * split / p.splits);
+                const int kb1 = (int)((long long)p.kblocks * (split + 1) / p.splits);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+                    tma_load_2d(smem_a + stage * A_BYTES, &map_a, &full[stage], kb * BK, a0);
+                    tma_load_2d(smem_b + stage * Cfg::B_BYTES, &map_b, &full[stage], kb * BK, b0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // Do not leave while copies may still be in flight: wait until the consumer released every stage.
+            for (int s = 0; s < STAGES && ok; ++s) {
+                if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) break;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
+                const int split = w % p.splits;
+                const int kb0 = (int)((long long)p.kblocks * split / p.splits);
+                const int kb1 = (int)((long long)p.kblocks * (split + 1) / p.splits);
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * A_BYTES));
+                    const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * Cfg::B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // the next 16 K elements are 32 bytes further along the swizzled row
+                        umma_bf16(d_addr, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);        // frees the stage when these instructions have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[acc]);           // the accumulator is complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        const int q = warp & 3;                        // the TMEM lane quarter this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
+            const int split = w % p.splits, tile = w / p.splits;
+            const int a0 = (tile % p.a_tiles) * BM, b0 = (tile / p.a_tiles) * BN;
+            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
+            tc_fence_after();
+            const int a = a0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const size_t split_off = (size_t)split * (size_t)p.split_stride;
+            constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += CH) {
+                uint32_t r[CH];
+                if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
+                tmem_ld_wait();
+                if (a < p.rows_a) {
+                    if (!p.swapped) {
+                        const size_t base = split_off + (size_t)a * p.ld + (size_t)(b0 + c);
+                        const bool full_chunk = (b0 + c + CH <= p.rows_b);
+                        if (p.out_bf16) {
+                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
+                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                                for (int j = 0; j < CH; j += 8) {
+                                    uint4 v;
+                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
+                                    *(uint4*)(o + j) = v;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j)
+                                    if (b0 + c + j < p.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        } else {
+                            float* o = (float*)p.out + base;
+                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                                for (int j = 0; j < CH; j += 4)
+                                    *(uint4*)(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j)
+                                    if (b0 + c + j < p.rows_b) o[j] = __uint_as_float(r[j]);
+                            }
+                        }
+                    } else {
+                        // transposed: this thread's accumulator row is output feature a; lanes are neighbours in a
+                        if (p.out_bf16) {
+                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + split_off + a;
+#pragma unroll
+                            for (int j = 0; j < CH; ++j)
+                                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        } else {
+                            float* o = (float*)p.out + split_off + a;
+#pragma unroll
+                            for (int j = 0; j < CH; ++j)
+                                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix seen as boxes of box_rows x 64 elements, 128-byte swizzle, zero fill
+// outside.  Maps are cached: weights and workspace buffers keep their addresses.
+bool make_map(CUtensorMap* out, const void* ptr, int rows, int K, int box_rows) {
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(ptr, rows, K, box_rows);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return true;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return n;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+    using Cfg = TileConfig<BN>;
+    static bool configured = false;
+    auto kernel = gemm_tcgen05_kernel<BN>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+            return fail(PH_ERR_LAUNCH, "gemm_tcgen05: cannot reserve %d bytes of shared memory", Cfg::SMEM_BYTES);
+        configured = true;
+    }
+    const int work = p.a_tiles * p.b_tiles * p.splits;
+    int grid = sm_count();
+    if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+    if (work < grid) grid = work;
+    kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    return check_launch("gemm_tcgen05");
+}
+
+}  // namespace
+
+PH_DEFINE_LAST_ERROR(ph_gemm100)
+
+// out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
+// side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).
+PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
+                                   int swapped, int block_n, int splits, int max_ctas, int* error_flag,
+                                   cudaStream_t stream) {
+    if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: bad arguments (M %d, N %d, K %d)", M, N, K);
+    if (K % 8) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05: operands must be 16-byte aligned");
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1 || splits > kblocks) return fail(PH_ERR_ARG, "gemm_tcgen05: %d splits for %d blocks of K", splits, kblocks);
+    if (splits > 1 && out_dtype != PH_F32) return fail(PH_ERR_ARG, "gemm_tcgen05: partial results are float32");
+    const void* a = swapped ? w : x;
+    const void* b = swapped ? x : w;
+    const int rows_a = swapped ? N : M, rows_b = swapped ? M : N;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, a, rows_a, K, BM) || !make_map(&mb, b, rows_b, K, block_n))
+        return fail(PH_ERR_LAUNCH, "gemm_tcgen05: cuTensorMapEncodeTiled failed (rows %d / %d, K %d)", rows_a, rows_b, K);
+    GemmParams p;
+    p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
+    p.a_tiles = (rows_a + BM - 1) / BM; p.b_tiles = (rows_b + block_n - 1) / block_n;
+    p.splits = splits; p.kblocks = kblocks;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.ld = N;
+    p.split_stride = (long long)M * N; p.error_flag = error_flag;
+    switch (block_n) {
+        case 16: return launch<16>(ma, mb, p, max_ctas, stream);
+        case 32: return launch<32>(ma, mb, p, max_ctas, stream);
+        case 64: return launch<64>(ma, mb, p, max_ctas, stream);
+        case 128: return launch<128>(ma, mb, p, max_ctas, stream);
+        case 256: return launch<256>(ma, mb, p, max_ctas, stream);
+        default: return fail(PH_ERR_ARG, "gemm_tcgen05: block_n %d is not one of 16, 32, 64, 128, 256", block_n);
+    }
+}

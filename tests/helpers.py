@@ -88,3 +88,99 @@ class TraceRun:
         self.proc.stdin.close()
         rc = self.proc.wait(timeout=60)
         assert rc == 0, f"trace_run exited with {rc}"
+
+
+# ---- replay schedules --------------------------------------------------------------------------------
+
+def schedule_whole(requests):
+    """Each request alone and whole: one step each."""
+    steps = []
+    for rid, toks in requests.items():
+        steps.append(([(rid, toks, list(range(len(toks))))], [rid]))
+    return steps
+
+
+def schedule_tail(requests, tail=32):
+    """Most of a request in one step, its last ``tail`` tokens one by one."""
+    steps = []
+    for rid, toks in requests.items():
+        head = max(len(toks) - tail, 0)
+        if head:
+            steps.append(([(rid, toks[:head], list(range(head)))], []))
+        for i in range(head, len(toks)):
+            steps.append(([(rid, toks[i:i + 1], [0])], [rid] if i == len(toks) - 1 else []))
+    return steps
+
+
+def schedule_portions(requests, sizes=(13, 2, 8, 3, 2, 5, 1, 21, 2, 2, 34, 1, 7)):
+    """Portions of changing size, down to two tokens (and single ones)."""
+    steps = []
+    for rid, toks in requests.items():
+        i, k = 0, 0
+        while i < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - i)
+            k += 1
+            steps.append(([(rid, toks[i:i + n], list(range(n)))], [rid] if i + n == len(toks) else []))
+            i += n
+    return steps
+
+
+def schedule_mixed(requests, max_live=4, seed=0, prompt_frac=0.6):
+    """Up to ``max_live`` live requests: portions of the prompts of some beside single tokens of others;
+    some requests sit a step out; a finished request ends and the next one joins."""
+    import random
+    rng = random.Random(seed)
+    order = list(requests)
+    pos = {rid: 0 for rid in order}
+    prompt_len = {rid: max(1, int(len(requests[rid]) * prompt_frac)) for rid in order}
+    live, nxt, steps = [], 0, []
+    while nxt < len(order) or live:
+        while len(live) < max_live and nxt < len(order):
+            live.append(order[nxt]); nxt += 1
+        entries, end = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                    # left out of this step
+            toks, p = requests[rid], pos[rid]
+            if p < prompt_len[rid]:
+                n = min(rng.choice([2, 3, 5, 8, 13, 16, 17, 31]), prompt_len[rid] - p)
+            else:
+                n = 1
+            n = min(n, len(toks) - p)
+            entries.append((rid, toks[p:p + n], list(range(n))))
+            pos[rid] = p + n
+            if pos[rid] == len(toks):
+                end.append(rid); live.remove(rid)
+        if entries:
+            steps.append((entries, end))
+    return steps
+
+
+def run_schedule(step_fn, release_fn, steps):
+    """Run ``steps`` and gather, per request, the logits of every position in order."""
+    out = {}
+    for k, (entries, end) in enumerate(steps):
+        logits = step_fn(k, entries, end)
+        row = 0
+        for rid, toks, want in entries:
+            n = len(want)
+            if n:
+                out.setdefault(rid, []).append(logits[row:row + n].clone())
+                row += n
+        if release_fn:
+            for rid in end:
+                release_fn(rid)
+    return {rid: torch.cat(parts) for rid, parts in out.items()}
+
+
+def engine_runner(engine):
+    from purhie_b200.engine import StepEntry
+
+    def step(k, entries, end):
+        for rid, _, _ in entries:
+            if not engine.has_request(rid):
+                engine.add_request(rid)
+        lg = engine.step([StepEntry(rid, toks, want) for rid, toks, want in entries])
+        return None if lg is None else lg.float().cpu()
+
+    return step, engine.release

@@ -1,0 +1,194 @@
+"""Each kernel alone against a plain float64/float32 PyTorch restatement, at sizes other than the engine's
+(GPU).  Sizes are deliberately awkward: widths and vocabularies that are no power of two, row counts that
+do not fill tiles."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def rel(got, ref):
+    return ((got.double() - ref.double()).abs().max() / ref.double().abs().max().clamp_min(1e-30)).item()
+
+
+# ---- matrix products -----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 40, 24), (5, 100, 96), (64, 64, 64), (70, 130, 50), (200, 257, 333)])
+@pytest.mark.parametrize("xd,wd,yd", [(torch.float32, torch.float32, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                      (torch.float32, torch.bfloat16, torch.float32)])
+def test_gemm_simple(M, N, K, xd, wd, yd):
+    from purhie_b200.csrc import ops
+    x, w = rnd(M, K, dtype=xd, seed=1), rnd(N, K, dtype=wd, seed=2)
+    out = torch.full((M, N), float("nan"), dtype=yd, device=DEV)
+    ops.gemm_simple(x, w, out)
+    ref = x.double() @ w.double().T
+    assert rel(out, ref) < (1e-5 if yd == torch.float32 else 6e-3)
+
+
+def test_gemm_simple_rows_do_not_depend_on_the_batch():
+    from purhie_b200.csrc import ops
+    x, w = rnd(150, 200, seed=3), rnd(90, 200, seed=4)
+    full = torch.empty(150, 90, device=DEV)
+    ops.gemm_simple(x, w, full)
+    for lo, hi in ((0, 1), (17, 18), (64, 150), (3, 70)):
+        part = torch.empty(hi - lo, 90, device=DEV)
+        ops.gemm_simple(x[lo:hi].contiguous(), w, part)
+        assert torch.equal(part, full[lo:hi])
+
+
+@pytest.mark.parametrize("M,N,K,swapped,block_n,splits", [
+    (128, 256, 64, False, 256, 1),          # one tile, one block of K
+    (128, 256, 512, False, 256, 1),         # the stage ring wraps
+    (300, 520, 200, False, 256, 1),         # ragged tiles on every side, K not a multiple of 64
+    (2048, 1024, 1024, False, 256, 1),      # many tiles per CTA: both accumulator buffers in use
+    (130, 136, 72, False, 128, 1),
+    (129, 72, 1000, False, 64, 1),
+    (1, 128, 64, True, 16, 1),              # one token
+    (8, 384, 256, True, 16, 1),
+    (8, 1000, 4096, True, 16, 8),           # decode shape: K split over CTAs, partial sums
+    (33, 520, 1000, True, 64, 3),
+    (64, 300, 328, True, 64, 2),
+    (100, 264, 512, True, 128, 1),
+    (17, 96, 96, True, 32, 1),
+    (200, 260, 136, True, 256, 1),
+])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05(M, N, K, swapped, block_n, splits, out_dtype):
+    from purhie_b200.csrc import gemm100
+    if splits > 1 and out_dtype != torch.float32:
+        pytest.skip("partial sums are float32")
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=5), rnd(N, K, dtype=torch.bfloat16, seed=6)
+    out = torch.full((splits, M, N) if splits > 1 else (M, N), float("nan"), dtype=out_dtype, device=DEV)
+    gemm100.gemm(x, w, out, swapped=swapped, block_n=block_n, splits=splits)
+    gemm100.check_errors(DEV)
+    got = out.double().sum(0) if splits > 1 else out.double()
+    ref = x.double() @ w.double().T
+    assert not torch.isnan(got).any()
+    assert rel(got, ref) < (2e-5 if out_dtype == torch.float32 else 5e-3)
+
+
+def test_gemm_tcgen05_against_the_plain_kernel_and_on_few_ctas():
+    from purhie_b200.csrc import gemm100, ops
+    x, w = rnd(384, 320, dtype=torch.bfloat16, seed=7), rnd(700, 320, dtype=torch.bfloat16, seed=8)
+    a, b, c = (torch.empty(384, 700, device=DEV) for _ in range(3))
+    gemm100.gemm(x, w, a, swapped=False, block_n=256)
+    gemm100.gemm(x, w, c, swapped=False, block_n=256, max_ctas=2)       # every CTA walks many tiles
+    ops.gemm_simple(x, w, b)
+    gemm100.check_errors(DEV)
+    assert rel(a, b) < 2e-5 and torch.equal(a, c)
+
+
+def test_gemm_tcgen05_refuses_what_tma_cannot_address():
+    from purhie_b200.csrc import gemm100
+    from purhie_b200.csrc.ops import KernelError
+    x, w = rnd(4, 100, dtype=torch.bfloat16), rnd(32, 100, dtype=torch.bfloat16)        # K % 8 != 0
+    assert not gemm100.supports(w)
+    with pytest.raises(KernelError):
+        gemm100.gemm(x, w, torch.empty(4, 32, device=DEV), swapped=True, block_n=16)
+
+
+# ---- norms, activation, embedding -----------------------------------------------------------------------
+
+@pytest.mark.parametrize("T,E", [(1, 96), (7, 1000), (33, 4096), (3, 12289)])
+@pytest.mark.parametrize("yd", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(T, E, yd):
+    from purhie_b200.csrc import ops
+    x, add, w = rnd(T, E, seed=1, scale=2.0), rnd(3, T, E, seed=2), rnd(E, seed=3) * 0.1 + 1.0
+    x0 = x.clone()
+    y = torch.empty(T, E, dtype=yd, device=DEV)
+    ops.add_rmsnorm(x, add, w, 1e-5, y, add_splits=3)
+    v = x0.double() + add.double().sum(0)
+    ref = v / torch.sqrt((v * v).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert rel(x, v) < 1e-6
+    assert rel(y, ref) < (1e-5 if yd == torch.float32 else 5e-3)
+    # gathered rows: nothing is written back
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    x1 = x0.clone()
+    y2 = torch.empty(2, E, dtype=yd, device=DEV)
+    ops.add_rmsnorm(x1, add[0].contiguous().to(torch.bfloat16), w, 1e-5, y2, rows=rows)
+    v2 = (x0.double() + add[0].to(torch.bfloat16).double())[[T - 1, 0]]
+    ref2 = v2 / torch.sqrt((v2 * v2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    assert torch.equal(x1, x0) and rel(y2, ref2) < (1e-5 if yd == torch.float32 else 5e-3)
+
+
+def test_add_rmsnorm_row_result_is_independent_of_the_batch():
+    from purhie_b200.csrc import ops
+    x, w = rnd(40, 1000, seed=4), rnd(1000, seed=5)
+    y = torch.empty(40, 1000, device=DEV)
+    ops.add_rmsnorm(x.clone(), None, w, 1e-6, y)
+    y1 = torch.empty(1, 1000, device=DEV)
+    ops.add_rmsnorm(x[23:24].clone(), None, w, 1e-6, y1)
+    assert torch.equal(y1[0], y[23])
+
+
+@pytest.mark.parametrize("T,FF,splits", [(1, 224, 1), (9, 1000, 1), (5, 352, 3)])
+def test_swiglu(T, FF, splits):
+    from purhie_b200.csrc import ops
+    for dt, tol in ((torch.float32, 1e-6), (torch.bfloat16, 6e-3)):
+        gu = rnd(splits, T, 2 * FF, dtype=torch.float32 if splits > 1 else dt, seed=6, scale=2.0)
+        out = torch.empty(T, FF, dtype=dt, device=DEV)
+        ops.swiglu(gu, out, splits=splits)
+        s = gu.double().sum(0)
+        g, u = s[:, :FF], s[:, FF:]
+        assert rel(out, g / (1 + torch.exp(-g)) * u) < tol
+
+
+def test_embed_gather_and_cast():
+    from purhie_b200.csrc import ops
+    table = rnd(1000, 96, dtype=torch.bfloat16, seed=7)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 96, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+    back = torch.empty(5, 96, dtype=torch.bfloat16, device=DEV)
+    ops.cast(out, back)
+    assert torch.equal(back, table[ids.long()])
+
+
+# ---- sampling ------------------------------------------------------------------------------------------
+
+def test_argmax_lowest_id_wins_ties():
+    from purhie_b200.csrc import ops
+    l = rnd(6, 151937, seed=8)
+    l[0, 777] = l[0, 150000] = 50.0
+    l[1, 151936] = 60.0
+    l[2, 0] = 70.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(l, out)
+    ref = [int(torch.nonzero(r == r.max())[0]) for r in l]
+    assert out.tolist() == ref and ref[:3] == [777, 151936, 0]
+
+
+def test_sample_temperature_follows_the_distribution_and_the_host_chain():
+    from purhie_b200.csrc import ops
+    from purhie_b200.sampling import Sampler, SamplerParams
+    from plain import qwen3_plain as P
+    V = 1000
+    row = rnd(V, seed=9, scale=3.0)
+    n = 4096
+    logits = row[None, :].expand(n, V).contiguous()
+    g = torch.Generator().manual_seed(0)
+    u = torch.rand(n, generator=g, dtype=torch.float64)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits, torch.full((n,), 0.7, device=DEV), u.to(DEV), out)
+    p = P.temperature_probabilities(row.cpu().numpy(), 0.7)
+    counts = torch.bincount(out.long().cpu(), minlength=V).double() / n
+    assert (counts - torch.from_numpy(p)).abs().max() < 0.02
+    # the same uniform numbers give the tokens of the host chain
+    s = Sampler(SamplerParams.pure_temperature(0.7, seed=5))
+    s2 = Sampler(SamplerParams.pure_temperature(0.7, seed=5))
+    us = torch.tensor([s2.uniform() for _ in range(64)], dtype=torch.float64)
+    host = [s.sample(row.cpu().numpy()) for _ in range(64)]
+    dev = torch.empty(64, dtype=torch.int32, device=DEV)
+    ops.sample_temperature(logits[:64].contiguous(), torch.full((64,), 0.7, device=DEV), us.to(DEV), dev)
+    assert dev.tolist() == host

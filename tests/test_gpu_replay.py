@@ -1,0 +1,121 @@
+"""The engine against the plain implementation under every way of cutting the work (GPU).
+
+For each tiny configuration and for float32 and bfloat16: each request alone and whole; most of it in one
+step and the last 32 tokens one by one; portions of changing size down to two tokens; and up to four live
+requests mixed in one batch with so few pages that they are used again.  float32 must agree with the
+plain implementation to 1e-4 of the largest logit with the same argmax everywhere; bfloat16 to 3e-2, a
+different argmax only at a near tie.  Nothing is widened to pass.
+"""
+import pytest
+import torch
+
+from plain import qwen3_plain as P
+from helpers import (TINY, TraceRun, engine_runner, make_model, random_tokens, rel_err, run_schedule,
+                     same_top1_or_near_tie, schedule_mixed, schedule_portions, schedule_tail, schedule_whole)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [1, 5, 17, 33, 64, 97, 120], "B": [2, 40, 97, 16, 130, 9, 250], "C": [3, 70, 200, 31, 129, 48]}
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+_cache = {}
+
+
+def setup(name, dtype, tmp_path_factory):
+    """(model folder, requests, plain logits) for a configuration; weights stored in the run's dtype."""
+    key = (name, dtype)
+    if key not in _cache:
+        cfg_dict, init = TINY[name]
+        folder = tmp_path_factory.mktemp(f"model_{name}_{dtype}")
+        cfg = make_model(folder, cfg_dict, init, dtype)
+        reqs = {f"r{i}": random_tokens(n, cfg.vocab_size, 100 + i) for i, n in enumerate(LENGTHS[name])}
+        pc, pw = P.read_model(str(folder))
+        ref = {rid: P.forward(pc, pw, toks) for rid, toks in reqs.items()}
+        _cache[key] = (str(folder), reqs, ref, init["page_size"])
+    return _cache[key]
+
+
+def check(got, ref, dtype, what):
+    for rid in ref:
+        assert got[rid].shape == ref[rid].shape, (what, rid)
+        err = rel_err(got[rid], ref[rid])
+        assert err < TOL[dtype], f"{what} {rid}: relative error {err:.3e}"
+        if dtype == "float32":
+            assert torch.equal(got[rid].argmax(-1), ref[rid].argmax(-1).to(got[rid].device)), f"{what} {rid}: argmax"
+        else:
+            assert not same_top1_or_near_tie(got[rid], ref[rid]), f"{what} {rid}: argmax differs away from a tie"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype, tmp_path_factory):
+    from purhie_b200.engine import Engine
+    folder, reqs, ref, page = setup(name, dtype, tmp_path_factory)
+    longest = max(len(t) for t in reqs.values())
+    results = {}
+    for mode, steps, max_tokens in (
+            ("whole", schedule_whole(reqs), 256),
+            ("tail32", schedule_tail(reqs), 256),
+            ("portions", schedule_portions(reqs), 256),
+            # four live requests in a pool that cannot hold all requests at once: pages are used again
+            ("mixed", schedule_mixed(reqs, seed=3), 4 * (-(-longest // 64) * 64))):
+        eng = Engine.from_folder(folder, dtype=dtype, page_size=page, max_tokens=max_tokens, max_requests=4,
+                                 poison_cache=True)
+        step, release = engine_runner(eng)
+        results[mode] = run_schedule(step, release, steps)
+        check(results[mode], ref, dtype, f"{name}/{dtype}/{mode}")
+        eng.cache.check()
+        assert eng.cache.free_pages() == [g.allocator.num_pages for g in eng.cache.groups]
+    if dtype == "float32":
+        # the 32-bit path fixes the order of every sum: cutting changes nothing at all
+        for mode in ("tail32", "portions", "mixed"):
+            for rid in ref:
+                assert torch.equal(results[mode][rid], results["whole"][rid]), f"{name}/{mode}/{rid} not bit-equal"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path_factory, tmp_path):
+    """bin/trace_run as a user drives it: a subprocess, JSON lines in, .f32 files and ``done`` lines out."""
+    folder, reqs, ref, page = setup("B", dtype, tmp_path_factory)
+    tr = TraceRun(folder, dtype, tmp_path / "out", max_tokens=4 * 256, extra=["--page-size", str(page)])
+    try:
+        got = run_schedule(lambda k, entries, end: tr.step(k, entries, end), None, schedule_mixed(reqs, seed=11))
+    finally:
+        tr.close()
+    check(got, ref, dtype, f"trace_run/{dtype}")
+
+
+def test_first_tokens_and_long_decoding(tmp_path_factory):
+    """The first tokens of a sequence (positions 0, 1, 2 one by one) and 200 decoded tokens in a row."""
+    from purhie_b200.engine import Engine
+    for dtype in ("float32", "bfloat16"):
+        folder, reqs, ref, page = setup("B", dtype, tmp_path_factory)
+        toks = reqs["r6"]
+        eng = Engine.from_folder(folder, dtype=dtype, page_size=page, max_tokens=256, max_requests=2)
+        step, release = engine_runner(eng)
+        steps = [([("r6", toks[i:i + 1], [0])], []) for i in range(len(toks))]
+        got = run_schedule(step, release, steps)
+        check(got, {"r6": ref["r6"]}, dtype, f"token by token/{dtype}")
+
+
+def test_step_refuses_bad_batches_and_leaves_the_cache_alone(tmp_path_factory):
+    from purhie_b200.cache import OutOfPages
+    from purhie_b200.engine import Engine, StepEntry, StepError
+    folder, reqs, ref, page = setup("A", "float32", tmp_path_factory)
+    eng = Engine.from_folder(folder, dtype="float32", page_size=16, max_tokens=64, max_requests=2)
+    eng.add_request("a"); eng.add_request("b")
+    with pytest.raises(StepError):
+        eng.step([StepEntry("a", [1, 2, 999], [0])])                # token outside the vocabulary
+    with pytest.raises(StepError):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(StepError):
+        eng.step([StepEntry("zz", [1], [0])])
+    with pytest.raises(StepError):
+        eng.step([StepEntry("a", [1, 2], [2])])
+    with pytest.raises(StepError):
+        eng.step([StepEntry("a", list(range(129)), [])])             # past max_position_embeddings
+    eng.step([StepEntry("a", list(range(40)), [])])
+    free = eng.cache.free_pages()
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("b", list(range(10)), []), StepEntry("a", list(range(30)), [])])
+    assert eng.cache.free_pages() == free and eng.length("a") == 40 and eng.length("b") == 0
+    eng.cache.check()
