@@ -1,6 +1,83 @@
-"""Python face of the tensor-core attention kernels (attention_flash.cu)."""
+"""Python face of the tensor-core attention kernels (attention_flash.cu).
+
+A step's rows go two ways: segments of one token (decoding) through the split-key kernel, every other
+segment (a portion of a prompt) through the tiled kernel.  Both read keys and values from the pages.
+"""
 from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import ops
+from .ops import KernelError, call, register_signatures
+
+register_signatures("flash", {
+    "ph_attention_prefill": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "ph_attention_decode": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                            c_void_p],
+})
+
+BLOCK_KEYS = 64
+MAX_SPLITS = 32
+_sm_count = {}
 
 
 def supports(head_dim: int, group_size: int) -> bool:
-    return False
+    return head_dim in (64, 128) and 1 <= group_size <= 16
+
+
+def _sms(device) -> int:
+    key = torch.device(device)
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_count[key]
+
+
+def decode_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
+    """Splits of the key range so that about two CTAs per SM are busy; never more than there are key blocks."""
+    span = min(max_ctx, window) if window else max_ctx
+    blocks = max(1, -(-span // BLOCK_KEYS))
+    want = max(1, (2 * sms) // max(1, n_rows * num_kv_heads))
+    return max(1, min(want, blocks, MAX_SPLITS))
+
+
+def prefill(q, k_base, v_base, page_stride, page_size, block_table, seg_start, seg_ctx_len, tile_seg, tile_first,
+            n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+    call("flash", "ph_attention_prefill", q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), page_stride, page_size,
+         block_table.data_ptr(), block_table.shape[-1], seg_start.data_ptr(), seg_ctx_len.data_ptr(), tile_seg.data_ptr(),
+         tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim, int(window or 0), float(scale),
+         ops._stream())
+
+
+def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_rows, row_seg, positions, out, workspace, *,
+           num_heads, num_kv_heads, head_dim, window, scale, splits) -> None:
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = workspace.get("attn_part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
+        part_ml = workspace.get("attn_part_ml", (n_rows, num_heads, splits, 2), torch.float32)
+    call("flash", "ph_attention_decode", q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), page_stride, page_size,
+         block_table.data_ptr(), block_table.shape[-1], None if row_list is None else row_list.data_ptr(), n_rows,
+         row_seg.data_ptr(), positions.data_ptr(), None if part_o is None else part_o.data_ptr(),
+         None if part_ml is None else part_ml.data_ptr(), out.data_ptr(), num_heads, num_kv_heads, head_dim, splits,
+         int(window or 0), float(scale), ops._stream())
+
+
+def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+    """All rows of the step: q [T, HQ, D] bfloat16 -> out [T, HQ * D] bfloat16."""
+    for name, t in (("q", q), ("out", out), ("k", cache.k_base)):
+        if t.dtype != torch.bfloat16:
+            raise KernelError(f"attention_flash: {name} must be bfloat16")
+    if ctx.n_q_tiles:
+        prefill(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.seg_start,
+                ctx.seg_ctx_len, ctx.q_tile_seg, ctx.q_tile_first, ctx.n_q_tiles, out, num_heads=num_heads,
+                num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale)
+    if ctx.n_decode_rows:
+        splits = ctx.extra.get("decode_splits") or decode_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx,
+                                                                _sms(q.device), window)
+        decode(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.decode_rows,
+               ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace, num_heads=num_heads,
+               num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale, splits=splits)

@@ -18,7 +18,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages, OutOfSlots
 from ..config.base import ModelConfig, load_config, lookup_architecture
-from ..parts.context import GroupStep, StepContext, Workspace
+from ..parts.context import Q_TILE, GroupStep, StepContext, Workspace
 from ..parts.model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -176,12 +176,23 @@ class Engine:
             slots.append(cache.slot_of(e.request_id))
             want.extend(base + int(w) for w in e.want)
         T, S, G = len(tokens), len(entries), len(cache.groups)
+        decode_rows, tile_seg, tile_first, decode_max_ctx = [], [], [], 0
+        for s, n in enumerate(q_lens):
+            if n == 1:
+                decode_rows.append(seg_start[s])
+                decode_max_ctx = max(decode_max_ctx, ctx_lens[s])
+            else:
+                for first in range(0, n, Q_TILE):
+                    tile_seg.append(s)
+                    tile_first.append(first)
+        n_dec, n_tiles = len(decode_rows), len(tile_seg)
         widths = []
         for g in cache.groups:
             w = max(len(cache.block_table(e.request_id, g.index)) for e in entries)
             widths.append(max(table_width or 0, -(-w // 8) * 8))
         # one packed int32 buffer, one copy
-        sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * G
+        sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * G + \
+                [max(n_dec, 1), max(n_tiles, 1), max(n_tiles, 1)]
         total = sum(sizes)
         # two pinned buffers in turn: a buffer is rewritten only after the copy that last read it is done
         self._meta_turn ^= 1
@@ -202,6 +213,7 @@ class Engine:
         for g in cache.groups:
             for e in entries:
                 flat += cache.token_slots(e.request_id, g.index, cache.length(e.request_id), len(e.tokens))
+        flat += (decode_rows or [0]) + (tile_seg or [0]) + (tile_first or [0])
         host.copy_(torch.tensor(flat, dtype=torch.int32))
         dev = self.workspace.get("step_meta", (total,), torch.int32)
         dev.copy_(host, non_blocking=True)
@@ -214,7 +226,10 @@ class Engine:
         ctx = StepContext(T=T, S=S, token_ids=parts[0], positions=parts[1], row_seg=parts[2], seg_start=parts[3],
                           seg_ctx_len=parts[4], seg_slot=parts[5], q_lens=q_lens, ctx_lens=ctx_lens, groups=groups,
                           workspace=self.workspace, compute_dtype=self.dtype,
-                          decode_only=all(q == 1 for q in q_lens))
+                          decode_only=n_tiles == 0,
+                          decode_rows=None if n_tiles == 0 else parts[7 + 2 * G], n_decode_rows=n_dec,
+                          decode_max_ctx=decode_max_ctx, q_tile_seg=parts[8 + 2 * G], q_tile_first=parts[9 + 2 * G],
+                          n_q_tiles=n_tiles)
         return ctx, parts[6], len(want)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

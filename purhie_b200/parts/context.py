@@ -14,6 +14,9 @@ import torch
 from .base import Addend
 
 
+Q_TILE = 64        # rows of a query tile of the prefill attention kernel
+
+
 class Workspace:
     """Scratch tensors by name, reused from step to step and grown on demand.
 
@@ -82,6 +85,14 @@ class StepContext:
     workspace: Workspace
     compute_dtype: torch.dtype
     decode_only: bool = False
+    # rows of single-token segments (None when every row is one: the list is then 0 .. T-1)
+    decode_rows: Optional[torch.Tensor] = None
+    n_decode_rows: int = 0
+    decode_max_ctx: int = 0
+    # the other segments cut into tiles of Q_TILE rows: segment and first row (within the portion) of each tile
+    q_tile_seg: Optional[torch.Tensor] = None
+    q_tile_first: Optional[torch.Tensor] = None
+    n_q_tiles: int = 0
     extra: dict = field(default_factory=dict)
 
     @property

@@ -192,3 +192,156 @@ def test_sample_temperature_follows_the_distribution_and_the_host_chain():
     dev = torch.empty(64, dtype=torch.int32, device=DEV)
     ops.sample_temperature(logits[:64].contiguous(), torch.full((64,), 0.7, device=DEV), us.to(DEV), dev)
     assert dev.tolist() == host
+
+
+# ---- attention over pages ----------------------------------------------------------------------------------
+
+def paged_case(segs, HQ, HKV, D, page_size, dtype, seed=0, poison=True):
+    """segs: [(ctx_len, q_len)].  Returns everything the attention kernels take plus the dense K, V per segment.
+    Pages are handed out in a shuffled order and every slot that holds no key is NaN."""
+    import random
+    rng = random.Random(seed)
+    n_pages = sum(-(-c // page_size) for c, _ in segs) + 3
+    order = list(range(n_pages))
+    rng.shuffle(order)
+    pool = torch.full((n_pages, 1, 2, HKV, page_size, D), float("nan") if poison else 0.0, dtype=dtype, device=DEV)
+    width = max(-(-c // page_size) for c, _ in segs)
+    table = torch.full((len(segs), width), -1, dtype=torch.int32)
+    dense, rows_seg, positions, seg_start = [], [], [], [0]
+    for s, (ctx, ql) in enumerate(segs):
+        k, v = rnd(ctx, HKV, D, dtype=dtype, seed=seed * 100 + 2 * s), rnd(ctx, HKV, D, dtype=dtype, seed=seed * 100 + 2 * s + 1)
+        dense.append((k, v))
+        for b in range(-(-ctx // page_size)):
+            page = order.pop()
+            table[s, b] = page
+            n = min(page_size, ctx - b * page_size)
+            pool[page, 0, 0, :, :n] = k[b * page_size:b * page_size + n].transpose(0, 1)
+            pool[page, 0, 1, :, :n] = v[b * page_size:b * page_size + n].transpose(0, 1)
+        rows_seg += [s] * ql
+        positions += list(range(ctx - ql, ctx))
+        seg_start.append(seg_start[-1] + ql)
+    T = len(positions)
+    q = rnd(T, HQ, D, dtype=dtype, seed=seed * 100 + 99)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(q=q, pool=pool, k_base=pool[0, 0, 0], v_base=pool[0, 0, 1], page_stride=pool.stride(0), table=table.to(DEV),
+                row_seg=i32(rows_seg), positions=i32(positions), seg_start=i32(seg_start),
+                seg_ctx=i32([c for c, _ in segs]), dense=dense, T=T, segs=segs)
+
+
+def dense_attention(case, HQ, HKV, D, window, scale):
+    out = torch.zeros(case["T"], HQ, D, dtype=torch.float64)
+    row = 0
+    for (ctx, ql), (k, v) in zip(case["segs"], case["dense"]):
+        k, v = k.double().cpu(), v.double().cpu()
+        for i in range(ql):
+            z = ctx - ql + i
+            lo = max(0, z - window + 1) if window else 0
+            for h in range(HQ):
+                g = h // (HQ // HKV)
+                s = (k[lo:z + 1, g] @ case["q"][row, h].double().cpu()) * scale
+                p = torch.softmax(s, 0)
+                out[row, h] = p @ v[lo:z + 1, g]
+            row += 1
+    return out.view(case["T"], HQ * D)
+
+
+def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
+    from purhie_b200.csrc import ops
+    out = torch.full((case["T"], HQ * D), float("nan"), dtype=out_dtype, device=DEV)
+    ops.attention_generic(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
+                          case["row_seg"], case["positions"], out, num_heads=HQ, num_kv_heads=HKV, head_dim=D,
+                          window=window, scale=scale)
+    return out
+
+
+def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None):
+    from purhie_b200.csrc import flash
+    from purhie_b200.parts.context import Workspace
+    out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    tile_seg, tile_first, dec_rows, start = [], [], [], 0
+    for s, (ctx, ql) in enumerate(case["segs"]):
+        if ql == 1:
+            dec_rows.append(start)
+        else:
+            for f in range(0, ql, 64):
+                tile_seg.append(s); tile_first.append(f)
+        start += ql
+    i32 = lambda x: torch.tensor(x or [0], dtype=torch.int32, device=DEV)
+    if tile_seg:
+        flash.prefill(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
+                      case["seg_start"], case["seg_ctx"], i32(tile_seg), i32(tile_first), len(tile_seg), out,
+                      num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
+    if dec_rows:
+        max_ctx = max(c for c, ql in case["segs"] if ql == 1)
+        sp = splits or flash.decode_splits(len(dec_rows), HKV, max_ctx, 148, window)
+        flash.decode(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
+                     None if len(dec_rows) == case["T"] else i32(dec_rows), len(dec_rows), case["row_seg"],
+                     case["positions"], out, Workspace(DEV), num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window,
+                     scale=scale, splits=sp)
+    return out
+
+
+@pytest.mark.parametrize("HQ,HKV,D,page_size,window", [
+    (4, 2, 16, 16, None), (8, 2, 32, 8, 24), (6, 3, 48, 5, 7), (3, 1, 80, 16, None), (2, 2, 256, 32, 100)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(HQ, HKV, D, page_size, window, dtype):
+    segs = [(1, 1), (33, 33), (70, 1), (129, 17), (40, 2)]
+    case = paged_case(segs, HQ, HKV, D, page_size, dtype, seed=1)
+    scale = 1.0 / math.sqrt(D)
+    out = run_generic(case, HQ, HKV, D, page_size, window, scale, dtype)
+    ref = dense_attention(case, HQ, HKV, D, window, scale)
+    assert rel(out.cpu(), ref) < (2e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("HQ,HKV,D,page_size,window", [
+    (8, 2, 128, 16, None), (4, 4, 64, 16, None), (6, 2, 64, 8, 40), (16, 1, 128, 64, 200), (32, 8, 128, 16, None),
+    (2, 1, 128, 3, 65)])
+def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
+    # portions that start mid-page, cross many blocks, end inside a tile; decode rows short and long
+    segs = [(1, 1), (64, 64), (200, 130), (300, 1), (65, 2), (700, 1), (513, 257), (63, 1), (128, 1)]
+    case = paged_case(segs, HQ, HKV, D, page_size, torch.bfloat16, seed=2)
+    scale = 1.0 / math.sqrt(D)
+    ref = dense_attention(case, HQ, HKV, D, window, scale)
+    out = run_flash(case, HQ, HKV, D, page_size, window, scale)
+    assert not torch.isnan(out.float()).any()
+    assert rel(out.cpu(), ref) < 1e-2
+    plain = run_generic(case, HQ, HKV, D, page_size, window, scale, torch.bfloat16)
+    assert rel(out.cpu(), plain.cpu()) < 1e-2
+    for sp in (1, 3, 32):                                  # any number of splits, more than there are blocks too
+        o2 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp)
+        assert rel(o2.cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "flash"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
+    """Random keys would hide a lost key among hundreds: make one key match the query so that it carries all the
+    weight, then put it first in the context, on a page's edge, just inside and just outside the window."""
+    HQ, HKV, D, ps = 4, 2, 64, 16
+    scale = 1.0 / math.sqrt(D)
+    dtype = torch.float32 if kernel == "generic32" else torch.bfloat16
+    ctx = 600
+    for window, key_pos, visible in [(None, 0, True), (None, 15, True), (None, 16, True), (None, 599, True),
+                                     (100, 500, True), (100, 499, False), (100, 599, True), (584, 16, True), (584, 15, False)]:
+        for ql in (1, 90):                       # the last row is a decode row or the end of a portion
+            case = paged_case([(ctx, ql)], HQ, HKV, D, ps, dtype, seed=3)
+            k, v = case["dense"][0]
+            qrow = case["T"] - 1
+            spike = torch.zeros(D, device=DEV); spike[5] = 60.0
+            case["q"][qrow, :] = spike.to(dtype)
+            page, off = int(case["table"][0, key_pos // ps]), key_pos % ps
+            case["pool"][page, 0, 0, :, off] = spike.to(dtype)       # K[key_pos] for both kv heads
+            k[key_pos] = spike.to(dtype)
+            marker = torch.full((D,), 7.0, device=DEV)
+            case["pool"][page, 0, 1, :, off] = marker.to(dtype)      # V[key_pos]
+            v[key_pos] = marker.to(dtype)
+            if kernel == "flash":
+                out = run_flash(case, HQ, HKV, D, ps, window, scale)
+            else:
+                out = run_generic(case, HQ, HKV, D, ps, window, scale, dtype)
+            got = out[qrow].float().view(HQ, D)
+            if visible:
+                assert (got - 7.0).abs().max() < 0.05, (kernel, window, key_pos, ql)
+            else:
+                assert got.abs().max() < 4.0, (kernel, window, key_pos, ql)
+            ref = dense_attention(case, HQ, HKV, D, window, scale)
+            assert rel(out.cpu(), ref) < (1e-5 if dtype == torch.float32 else 1e-2)
