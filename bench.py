@@ -1,0 +1,253 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on
+the device over exactly K decode steps after W warm-up steps; ``e2e`` is the same through the Python entry
+point (purhie_b200.api) with host token ids in and sampled tokens out every step; ``prefill`` is one
+2,048-token prompt; ``roofline`` is the decode step's bytes (every weight once plus the live requests'
+cache) over its time; ``points`` holds decode at batch 1 and 64.  Token ids are uniform random (synthetic).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE configs[2]: the Qwen3-8B shape
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, intermediate_size=12288,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+                max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
+CONTEXT, PREFIX, PREFILL_TOKENS, SEED = 4096, 2048, 2048, 2
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+                    "source": "measured"}
+        except (ValueError, KeyError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                clocks.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference is a HIP engine for AMD gfx1151 (Makefile + hipcc, GGUF models); it has no Python "
+                      "package to install (pip finds neither setup.py nor pyproject.toml) and no CUDA path"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                    help="fewer layers than the configuration's 36 (named in config); layer sizes stay")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from purhie_b200.api import GenOptions, load_model_random
+    from purhie_b200.config import Qwen3Config
+    from purhie_b200.csrc import gemm100, ops
+    from purhie_b200.engine import StepEntry
+    from purhie_b200.sampling import SamplerParams
+
+    cfg = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=args.layers))
+    pk = peaks()
+    dev = "cuda:0"
+    model = load_model_random(cfg, SEED, "bfloat16", dev)
+    max_batch = max(64, args.batch)
+    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 1, page_size=16,
+                        kv_tokens=max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64)
+    eng = model.engine
+    eng.release(("seq", 0))
+    g = torch.Generator().manual_seed(SEED)
+    ids = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record(); fn(); e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    # ---- prefill of one 2,048-token prompt ----------------------------------------------------------
+    prompt = ids(PREFILL_TOKENS)
+
+    def prefill_once():
+        eng.add_request("prefill")
+        eng.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+        eng.release("prefill")
+
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = timed(prefill_once, 5)
+    T, E, FF, V = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    qw, kvw, D = cfg.q_width, cfg.kv_width, cfg.head_dim
+    layer_mm = E * (qw + 2 * kvw) + qw * E + 3 * E * FF
+    prefill_flops = cfg.num_hidden_layers * (2.0 * T * layer_mm + 4.0 * cfg.num_attention_heads * D * T * (T + 1) / 2) + 2.0 * V * E
+    prefill = {"value": round(T / prefill_ms * 1e3, 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(prefill_flops / (prefill_ms * 1e-3) / 1e12, 1), "peak": pk["source"]}
+
+    # ---- prefixes of 2,048 tokens for every request ---------------------------------------------------
+    for i in range(max_batch):
+        eng.add_request(i)
+        eng.step([StepEntry(i, ids(PREFIX), [])])
+    torch.cuda.synchronize()
+
+    weight_bytes = 2.0 * (cfg.num_hidden_layers * layer_mm + V * E)
+    kv_bytes_per_token = 2.0 * 2 * cfg.num_hidden_layers * kvw
+
+    def decode_run(batch, steps, warmup):
+        toks = [ids(steps + warmup) for _ in range(batch)]
+        step_no = [0]
+
+        def one():
+            k = step_no[0]
+            step_no[0] += 1
+            eng.step([StepEntry(i, [toks[i][k]], [0]) for i in range(batch)])
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        ctx0 = eng.length(0)
+        before = ops.launches
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            one()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / steps
+        bytes_step = weight_bytes + batch * (ctx0 + steps / 2.0) * kv_bytes_per_token
+        return ms, ops.launches - before, bytes_step
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms_step, launches, bytes_step = decode_run(args.batch, args.steps, args.warmup)
+    clocks = sampler.stop()
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            ms_b, _, by = decode_run(b, min(args.steps, 32), 3)
+            points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
+            points[f"decode_b{b}_hbm_frac"] = round(by / (ms_b * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
+    gemm100.check_errors(dev)
+
+    # ---- end to end through the Python entry point ------------------------------------------------------
+    for i in range(max_batch):
+        eng.release(i)
+    model._seqs = {}
+    streams = []
+    opts = GenOptions(sampler=SamplerParams.greedy(), max_new_tokens=args.steps + args.warmup + 8, ignore_eog=True)
+    for i in range(args.batch):
+        seq = model.seq_new()
+        model.seq_select(seq)
+        streams.append(model.stream_begin(ids(PREFIX), opts))
+    for _ in range(args.warmup):
+        model.stream_step_batch(streams)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    s.record()
+    for _ in range(args.steps):
+        model.stream_step_batch(streams)
+    e.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / args.steps
+    h2d = eng.last_upload_bytes                                 # the step's packed int32 metadata (ids, positions, tables)
+    e2e = {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+
+    value = args.batch / ms_step * 1e3
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 from 2,048-token prefixes (Qwen3-8B shape)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape, random weights seed 2", "global_batch": args.batch, "seq_len": PREFIX,
+                   "context": CONTEXT, "parallelism": "single GPU", "layers": args.layers,
+                   "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": E, "q_heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": D, "intermediate": FF, "vocab": V,
+                   "kv_page_tokens": 16, "kv_dtype": "bf16", "l2": "weights (>=16 GB) exceed L2 every step",
+                   "cuda_graphs": True, "prefill_tokens": PREFILL_TOKENS},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -107,15 +107,18 @@ class Stream:
 
 
 class Model:
-    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", options: Optional[dict] = None):
-        try:
-            arch, config = load_config(model_dir)
-            self._decoder = DecoderModel(arch.build_spec(config), parse_dtype(dtype), options)
-            self._decoder.load(model_dir, device)
-        except (ConfigError, ValueError, OSError) as e:
-            raise InferenceError(ERR_MODEL_LOAD, str(e)) from e
-        self.model_dir, self.config, self.device = model_dir, config, device
-        self.eos_ids = _eos_ids(model_dir)
+    def __init__(self, model_dir: Optional[str], dtype="bfloat16", device="cuda:0", options: Optional[dict] = None,
+                 decoder: Optional[DecoderModel] = None, config=None):
+        if decoder is None:
+            try:
+                arch, config = load_config(model_dir)
+                decoder = DecoderModel(arch.build_spec(config), parse_dtype(dtype), options)
+                decoder.load(model_dir, device)
+            except (ConfigError, ValueError, OSError) as e:
+                raise InferenceError(ERR_MODEL_LOAD, str(e)) from e
+        self._decoder = decoder
+        self.model_dir, self.config, self.device = model_dir or "random", config, device
+        self.eos_ids = _eos_ids(model_dir) if model_dir else []
         self.engine: Optional[Engine] = None
         self._seed = 0
         self._prefill_batch = 1024
@@ -125,7 +128,8 @@ class Model:
         self.last_prompt_stats = (0, 0)
 
     # ---- set-up ------------------------------------------------------------------------------------
-    def kv_cache_init(self, n_ctx: int, max_sequences: int = 4, page_size: int = 16, kv_tokens: Optional[int] = None) -> int:
+    def kv_cache_init(self, n_ctx: int, max_sequences: int = 4, page_size: int = 16, kv_tokens: Optional[int] = None,
+                      **engine_options) -> int:
         """A cache for sequences of up to ``n_ctx`` tokens.  The pool holds ``kv_tokens`` tokens in all
         (default: ``max_sequences`` full contexts)."""
         if n_ctx < 1:
@@ -135,7 +139,7 @@ class Model:
                                                   f"{self._decoder.spec.max_position}")
         per_seq = -(-n_ctx // page_size) * page_size
         self.engine = Engine(self._decoder, self.config, page_size=page_size, max_tokens=kv_tokens or per_seq * max_sequences,
-                             max_requests=max_sequences, device=self.device)
+                             max_requests=max_sequences, device=self.device, **engine_options)
         self._n_ctx = n_ctx
         self._seqs = {0: _Sequence(0)}
         self.engine.add_request(("seq", 0))
@@ -420,6 +424,22 @@ class Model:
         eng.add_request(("seq", 0))
         self._current = 0
         return [r.output for r in reqs]
+
+
+def load_model_random(config, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02, scale_low: float = 1.0,
+                      scale_high: float = 1.0, options: Optional[dict] = None) -> Model:
+    """A model of ``config`` (a typed configuration) with seeded random weights made on the device."""
+    from .config.base import lookup_architecture
+    from .weights.loader import device_dtype
+    from .weights.random_init import random_tensor
+    dt = parse_dtype(dtype)
+    decoder = DecoderModel(lookup_architecture(config.architecture).build_spec(config), dt, options)
+    tensors = {}
+    for name, spec in decoder.tensor_specs().items():
+        t = random_tensor(spec, seed, std, scale_low, scale_high, device=device)
+        tensors[name] = t.to(device_dtype(torch.bfloat16, spec.role, dt))
+    decoder.bind(tensors, device)
+    return Model(None, dtype, device, options, decoder=decoder, config=config)
 
 
 def load_model(path: str, dtype="bfloat16", device="cuda:0", options: Optional[dict] = None) -> Model:

@@ -413,9 +413,13 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
 }
 
-template <typename K> int set_smem(K kernel, int bytes) {
-    if (bytes > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+// Raise a kernel's dynamic shared-memory limit, once per kernel (TAG tells kernels of one signature apart).
+template <int TAG, typename K> int set_smem(K kernel, int bytes) {
+    static bool done = false;
+    if (done || bytes <= 48 * 1024) return PH_OK;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
         return fail(PH_ERR_LAUNCH, "attention_flash: cannot reserve %d bytes of shared memory", bytes);
+    done = true;
     return PH_OK;
 }
 
@@ -439,7 +443,7 @@ PH_EXPORT int ph_attention_prefill(const void* q, const void* k_base, const void
 #define LAUNCH(DD)                                                                                               \
     do {                                                                                                         \
         const int bytes = 64 * DD * 2 + 4 * BLOCK_KEYS * DD * 2;                                                 \
-        if (int rc = set_smem(attention_prefill_kernel<DD>, bytes)) return rc;                                   \
+        if (int rc = set_smem<2 * DD>(attention_prefill_kernel<DD>, bytes)) return rc;                                   \
         attention_prefill_kernel<DD><<<grid, THREADS, bytes, stream>>>(                                          \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_base, (const __nv_bfloat16*)v_base, page_stride,    \
             page_size, block_table, table_stride, seg_start, seg_ctx_len, tile_seg, tile_first,                  \
@@ -468,7 +472,7 @@ PH_EXPORT int ph_attention_decode(const void* q, const void* k_base, const void*
     do {                                                                                                         \
         const int kv_bytes = 4 * BLOCK_KEYS * DD * 2, red_bytes = 4 * 16 * (DD + 2) * 4;                         \
         const int bytes = 16 * DD * 2 + (kv_bytes > red_bytes ? kv_bytes : red_bytes);                           \
-        if (int rc = set_smem(attention_decode_kernel<DD>, bytes)) return rc;                                    \
+        if (int rc = set_smem<2 * DD + 1>(attention_decode_kernel<DD>, bytes)) return rc;                                    \
         attention_decode_kernel<DD><<<grid, THREADS, bytes, stream>>>(                                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_base, (const __nv_bfloat16*)v_base, page_stride,    \
             page_size, block_table, table_stride, row_list, row_seg, positions, part_o, part_ml,                 \

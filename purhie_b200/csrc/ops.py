@@ -86,8 +86,13 @@ def register_signatures(lib_name: str, table: dict) -> None:
     _SIGNATURES.setdefault(lib_name, {}).update(table)
 
 
+launches = 0          # launcher calls so far (a captured graph replays the calls counted while it was captured)
+
+
 def call(lib_name: str, fn_name: str, *args) -> None:
+    global launches
     f, err = _fn(lib_name, fn_name)
+    launches += 1
     rc = f(*args)
     if rc != 0:
         raise KernelError(err().decode("utf-8", "replace") or f"{fn_name} failed with status {rc}")

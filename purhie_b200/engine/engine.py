@@ -56,13 +56,40 @@ def parse_dtype(dtype) -> torch.dtype:
         raise ValueError(f"dtype {dtype!r} is not supported (bfloat16 or float32)") from None
 
 
+@dataclass
+class _Layout:
+    flat: List[int]
+    sizes: List[int]
+    T: int
+    S: int
+    widths: List[int]
+    q_lens: List[int]
+    ctx_lens: List[int]
+    n_want: int
+    n_decode: int
+    n_tiles: int
+    decode_max_ctx: int
+
+
+@dataclass
+class _DecodeGraph:
+    workspace: Workspace
+    meta: torch.Tensor
+    graph: Optional[torch.cuda.CUDAGraph] = None
+    logits: Optional[torch.Tensor] = None
+    rows: Optional[torch.Tensor] = None
+    launches: int = 0
+
+
 class Engine:
     def __init__(self, model: DecoderModel, config: Optional[ModelConfig], *, page_size: int = 16,
                  max_tokens: int = 4096, max_requests: int = 4, num_pages=None, device="cuda:0",
-                 poison_cache: bool = False):
+                 poison_cache: bool = False, cuda_graphs: bool = True, max_graph_batch: int = 256,
+                 max_graphs: int = 24):
         """``model`` is bound to its weights already.  The cache holds ``max_tokens`` tokens per page group
         (each request's count rounded up to whole pages) for up to ``max_requests`` live requests;
-        ``num_pages`` overrides the page count (one number or one per group)."""
+        ``num_pages`` overrides the page count (one number or one per group).  With ``cuda_graphs`` a batch
+        of single tokens replays a captured graph of the model's launches."""
         if not torch.cuda.is_available():
             raise RuntimeError("purhie_b200 runs on a CUDA device only; no GPU is visible and there is no host path")
         self.model = model
@@ -82,6 +109,11 @@ class Engine:
         self.last_stats = StepStats()
         self._meta_host = [(None, None), (None, None)]
         self._meta_turn = 0
+        self.cuda_graphs = cuda_graphs
+        self.max_graph_batch = max_graph_batch
+        self.max_graphs = max_graphs
+        self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self.last_upload_bytes = 0
         from ..csrc.build import load_library
         for lib in model.required_libraries():          # compile what this model needs, now
             load_library(lib)
@@ -101,16 +133,8 @@ class Engine:
                     **kw) -> "Engine":
         """Random weights made directly on the device (no folder is written).  Values differ from those of
         :func:`purhie_b200.weights.write_random_model`, which draws on the host."""
-        from ..weights.loader import device_dtype
-        from ..weights.random_init import random_tensor
-        dt = parse_dtype(dtype)
-        arch = lookup_architecture(config.architecture)
-        model = DecoderModel(arch.build_spec(config), dt, options)
-        tensors = {}
-        for name, spec in model.tensor_specs().items():
-            t = random_tensor(spec, seed, std, scale_low, scale_high, device=device)
-            tensors[name] = t.to(device_dtype(torch.bfloat16, spec.role, dt))
-        model.bind(tensors, device)
+        from ..api import load_model_random
+        model = load_model_random(config, seed, dtype, device, std, scale_low, scale_high, options)._decoder
         return cls(model, config, device=device, **kw)
 
     # ---- requests --------------------------------------------------------------------------------
@@ -149,9 +173,9 @@ class Engine:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
 
-    def build_context(self, entries: Sequence[StepEntry], table_width: Optional[int] = None):
-        """Reserve pages and upload the batch's metadata.  Returns (ctx, want_rows, n_want)."""
-        cache, ps = self.cache, self.page_size
+    def _layout(self, entries: Sequence[StepEntry], table_width: Optional[int] = None) -> "_Layout":
+        """Reserve pages for the batch and lay its metadata out as one int32 buffer."""
+        cache = self.cache
         reserved = []
         try:
             for e in entries:
@@ -175,7 +199,7 @@ class Engine:
             q_lens.append(n)
             slots.append(cache.slot_of(e.request_id))
             want.extend(base + int(w) for w in e.want)
-        T, S, G = len(tokens), len(entries), len(cache.groups)
+        T, S = len(tokens), len(entries)
         decode_rows, tile_seg, tile_first, decode_max_ctx = [], [], [], 0
         for s, n in enumerate(q_lens):
             if n == 1:
@@ -185,25 +209,12 @@ class Engine:
                 for first in range(0, n, Q_TILE):
                     tile_seg.append(s)
                     tile_first.append(first)
-        n_dec, n_tiles = len(decode_rows), len(tile_seg)
         widths = []
         for g in cache.groups:
             w = max(len(cache.block_table(e.request_id, g.index)) for e in entries)
             widths.append(max(table_width or 0, -(-w // 8) * 8))
-        # one packed int32 buffer, one copy
-        sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * G + \
-                [max(n_dec, 1), max(n_tiles, 1), max(n_tiles, 1)]
-        total = sum(sizes)
-        # two pinned buffers in turn: a buffer is rewritten only after the copy that last read it is done
-        self._meta_turn ^= 1
-        buf, event = self._meta_host[self._meta_turn]
-        if buf is None or buf.numel() < total:
-            buf = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
-            event = torch.cuda.Event()
-        else:
-            event.synchronize()
-        self._meta_host[self._meta_turn] = (buf, event)
-        host = buf[:total]
+        sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * len(cache.groups) + \
+                [max(len(decode_rows), 1), max(len(tile_seg), 1), max(len(tile_seg), 1)]
         flat: List[int] = []
         flat += tokens + positions + row_seg + seg_start + ctx_lens + slots + (want if want else [0])
         for g, w in zip(cache.groups, widths):
@@ -214,40 +225,126 @@ class Engine:
             for e in entries:
                 flat += cache.token_slots(e.request_id, g.index, cache.length(e.request_id), len(e.tokens))
         flat += (decode_rows or [0]) + (tile_seg or [0]) + (tile_first or [0])
-        host.copy_(torch.tensor(flat, dtype=torch.int32))
-        dev = self.workspace.get("step_meta", (total,), torch.int32)
-        dev.copy_(host, non_blocking=True)
+        return _Layout(flat, sizes, T, S, widths, q_lens, ctx_lens, len(want), len(decode_rows), len(tile_seg),
+                       decode_max_ctx)
+
+    def _upload(self, flat: List[int], dev: torch.Tensor) -> None:
+        """One copy of the metadata to the device, through two pinned buffers used in turn: a buffer is
+        rewritten only after the copy that last read it is done."""
+        total = len(flat)
+        self.last_upload_bytes = 4 * total
+        self._meta_turn ^= 1
+        buf, event = self._meta_host[self._meta_turn]
+        if buf is None or buf.numel() < total:
+            buf = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
+            event = torch.cuda.Event()
+        else:
+            event.synchronize()
+        self._meta_host[self._meta_turn] = (buf, event)
+        buf[:total].copy_(torch.tensor(flat, dtype=torch.int32))
+        dev.copy_(buf[:total], non_blocking=True)
         event.record()
+
+    def _context(self, lay: "_Layout", dev: torch.Tensor, workspace: Workspace):
+        """The step context over the metadata in ``dev``.  Returns (ctx, want_rows)."""
+        G, S = len(self.cache.groups), lay.S
         parts, off = [], 0
-        for n in sizes:
+        for n in lay.sizes:
             parts.append(dev[off:off + n])
             off += n
-        groups = [GroupStep(parts[7 + i].view(S, widths[i]), parts[7 + G + i], ps) for i in range(G)]
-        ctx = StepContext(T=T, S=S, token_ids=parts[0], positions=parts[1], row_seg=parts[2], seg_start=parts[3],
-                          seg_ctx_len=parts[4], seg_slot=parts[5], q_lens=q_lens, ctx_lens=ctx_lens, groups=groups,
-                          workspace=self.workspace, compute_dtype=self.dtype,
-                          decode_only=n_tiles == 0,
-                          decode_rows=None if n_tiles == 0 else parts[7 + 2 * G], n_decode_rows=n_dec,
-                          decode_max_ctx=decode_max_ctx, q_tile_seg=parts[8 + 2 * G], q_tile_first=parts[9 + 2 * G],
-                          n_q_tiles=n_tiles)
-        return ctx, parts[6], len(want)
+        groups = [GroupStep(parts[7 + i].view(S, lay.widths[i]), parts[7 + G + i], self.page_size) for i in range(G)]
+        ctx = StepContext(T=lay.T, S=S, token_ids=parts[0], positions=parts[1], row_seg=parts[2], seg_start=parts[3],
+                          seg_ctx_len=parts[4], seg_slot=parts[5], q_lens=lay.q_lens, ctx_lens=lay.ctx_lens,
+                          groups=groups, workspace=workspace, compute_dtype=self.dtype, decode_only=lay.n_tiles == 0,
+                          decode_rows=None if lay.n_tiles == 0 else parts[7 + 2 * G], n_decode_rows=lay.n_decode,
+                          decode_max_ctx=lay.decode_max_ctx, q_tile_seg=parts[8 + 2 * G],
+                          q_tile_first=parts[9 + 2 * G], n_q_tiles=lay.n_tiles)
+        return ctx, parts[6]
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """Reserve pages and upload the batch's metadata.  Returns (ctx, want_rows, n_want)."""
+        lay = self._layout(entries)
+        dev = self.workspace.get("step_meta", (len(lay.flat),), torch.int32)
+        self._upload(lay.flat, dev)
+        ctx, want_rows = self._context(lay, dev, self.workspace)
+        return ctx, want_rows, lay.n_want
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted places, vocab] on the device in the order of the
-        entries and of each entry's ``want`` (None when nothing is wanted).  Raises :class:`OutOfPages`,
-        leaving everything as it was, when the cache cannot hold the batch."""
+        entries and of each entry's ``want`` (None when nothing is wanted); they live in scratch memory that
+        the next step reuses.  Raises :class:`OutOfPages`, leaving everything as it was, when the cache
+        cannot hold the batch."""
         entries = list(entries)
         if not entries:
             return None
         self._validate(entries)
-        ctx, want_rows, n_want = self.build_context(entries)
-        logits = self.model.forward(ctx, self.views, want_rows, n_want)
+        if self.cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
+            logits, T, n_want = self._decode_with_graph(entries)
+            q_lens = [1] * T
+        else:
+            ctx, want_rows, n_want = self.build_context(entries)
+            logits = self.model.forward(ctx, self.views, want_rows, n_want)
+            T, q_lens = ctx.T, ctx.q_lens
         for e in entries:
             self.cache.advance(e.request_id, len(e.tokens))
-        self.last_stats = StepStats(tokens=ctx.T, prompt_rows=sum(q for q in ctx.q_lens if q > 1),
-                                    decode_rows=sum(1 for q in ctx.q_lens if q == 1), wanted=n_want,
+        self.last_stats = StepStats(tokens=T, prompt_rows=sum(q for q in q_lens if q > 1),
+                                    decode_rows=sum(1 for q in q_lens if q == 1), wanted=n_want,
                                     pages_free=self.cache.free_pages())
         return logits
+
+    # ---- decoding through CUDA graphs --------------------------------------------------------------
+    def _decode_with_graph(self, entries: Sequence[StepEntry]):
+        """A batch of single tokens: the launches of the whole model are captured once per (batch size, block
+        table width, attention splits) and replayed.  Each graph owns its scratch memory and metadata buffer,
+        so nothing it points at ever moves."""
+        S = len(entries)
+        need = max(len(self.cache.block_table(e.request_id, g.index)) + 1 for e in entries for g in self.cache.groups) \
+            if self.cache.groups else 1
+        width = 8
+        while width < need:
+            width *= 2
+        # the graph computes every row's logits, so the layout (and its size) does not depend on what is wanted
+        lay = self._layout([StepEntry(e.request_id, e.tokens, [0]) for e in entries], table_width=width)
+        want = [i for i, e in enumerate(entries) if len(e.want)]
+        ctx_bucket = 256
+        while ctx_bucket < lay.decode_max_ctx:
+            ctx_bucket *= 2
+        key = (S, tuple(lay.widths), ctx_bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            g = _DecodeGraph(Workspace(self.device), torch.empty(len(lay.flat), dtype=torch.int32, device=self.device))
+            self._graphs[key] = g
+        self._upload(lay.flat, g.meta)
+        # every row's logits are computed; the wanted ones are picked afterwards
+        all_rows = torch.arange(S, dtype=torch.int32, device=self.device) if g.rows is None else g.rows
+        g.rows = all_rows
+        ctx, want_rows = self._context(lay, g.meta, g.workspace)
+        ctx.decode_max_ctx = ctx_bucket          # the number of attention splits must not change between replays
+        if g.graph is None:
+            # the first time: run the launches directly (this is the step's result, and whatever a kernel
+            # sets up on first use is set up), then capture the same launches for the next time
+            g.logits = self.model.forward(ctx, self.views, all_rows, S)
+            g.workspace.frozen = True
+            from ..csrc import ops
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.views, all_rows, S)
+            g.launches = ops.launches - before
+            ops.launches = before
+            g.graph = graph
+        else:
+            from ..csrc import ops
+            g.graph.replay()
+            ops.launches += g.launches
+        if len(want) == S:
+            return g.logits, S, S
+        if not want:
+            return None, S, 0
+        idx = torch.tensor(want, dtype=torch.long, device=self.device)
+        return g.logits.index_select(0, idx), S, len(want)
 
     # ---- sampling --------------------------------------------------------------------------------
     def sample(self, logits: torch.Tensor, samplers) -> List[int]:
