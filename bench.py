@@ -100,6 +100,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
+                    help="run one phase only, with few launches around it (for profiling under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -119,7 +121,9 @@ def main():
     pk = peaks()
     dev = "cuda:0"
     model = load_model_random(cfg, SEED, "bfloat16", dev)
-    max_batch = max(64, args.batch)
+    max_batch = args.batch if args.phase != "all" else max(64, args.batch)
+    if args.phase != "all":
+        args.no_points = True
     model.kv_cache_init(CONTEXT, max_sequences=max_batch + 1, page_size=16,
                         kv_tokens=max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64)
     eng = model.engine
@@ -146,9 +150,15 @@ def main():
         eng.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
         eng.release("prefill")
 
-    for _ in range(3):
-        prefill_once()
-    prefill_ms = timed(prefill_once, 5)
+    if args.phase == "decode":
+        prefill_ms = float("nan")
+    else:
+        for _ in range(3 if args.phase == "all" else 1):
+            prefill_once()
+        prefill_ms = timed(prefill_once, 5 if args.phase == "all" else 1)
+    if args.phase == "prefill":
+        print(json.dumps({"phase": "prefill", "ms": prefill_ms, "layers": args.layers}))
+        return 0
     T, E, FF, V = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     qw, kvw, D = cfg.q_width, cfg.kv_width, cfg.head_dim
     layer_mm = E * (qw + 2 * kvw) + qw * E + 3 * E * FF
@@ -201,6 +211,9 @@ def main():
             points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
             points[f"decode_b{b}_hbm_frac"] = round(by / (ms_b * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
     gemm100.check_errors(dev)
+    if args.phase == "decode":
+        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": ms_step, "layers": args.layers}))
+        return 0
 
     # ---- end to end through the Python entry point ------------------------------------------------------
     for i in range(max_batch):

@@ -52,6 +52,82 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     for (int i = threadIdx.x; i < E; i += NT) yr[i] = from_float<TY>(row_buf[i] * inv * weight[i]);
 }
 
+// The same with four consecutive elements per thread and all loads of a row in flight at once: a decode step
+// has a handful of rows, so the time of this kernel is the latency of its loads, not their volume.  E % 4 == 0,
+// every pointer 16-byte aligned (8 for bfloat16); the block has ceil(E / 4) threads rounded up to a warp, at
+// most 1024, so the order of the additions still depends on E only.
+template <typename T> struct Vec4 { };
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+template <typename TA, typename TY, int MAX_IT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
+                                       long long add_split_stride, const float* __restrict__ weight, float eps,
+                                       const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float* xr = x + (size_t)t * E;
+    float4 v[MAX_IT];
+    float ss = 0.0f;
+#pragma unroll
+    for (int it = 0; it < MAX_IT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < E) {
+            float4 acc = Vec4<float>::load(xr + i);
+            if (add) {
+                const TA* a = add + (size_t)t * E + i;
+                for (int s0 = 0; s0 < add_splits; s0 += 4) {      // four loads in flight, added in order
+                    float4 u[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        u[j] = s0 + j < add_splits ? Vec4<TA>::load(a + (size_t)(s0 + j) * add_split_stride)
+                                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (s0 + j < add_splits) { acc.x += u[j].x; acc.y += u[j].y; acc.z += u[j].z; acc.w += u[j].w; }
+                }
+                if (write_x) Vec4<float>::store(xr + i, acc);
+            }
+            v[it] = acc;
+            ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+        }
+    }
+    if (!weight) return;
+    // block sum in a fixed order: lanes, then warps
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (lane == 0) scratch[warp] = ss;
+    __syncthreads();
+    float tot = lane < nwarps ? scratch[lane] : 0.0f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / (float)E + eps);
+    TY* yr = y + (size_t)r * E;
+#pragma unroll
+    for (int it = 0; it < MAX_IT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < E) {
+            const float4 w = Vec4<float>::load(weight + i);
+            Vec4<TY>::store(yr + i, make_float4(v[it].x * inv * w.x, v[it].y * inv * w.y, v[it].z * inv * w.z, v[it].w * inv * w.w));
+        }
+    }
+}
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
                               int FF, long long total) {
@@ -93,6 +169,22 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
         return fail(PH_ERR_ARG, "add_rmsnorm: bad arguments (rows %d, E %d)", n_out, E);
     if (rows && write_x && add) return fail(PH_ERR_ARG, "add_rmsnorm: a gathered launch cannot write x back");
     if (n_out == 0) return PH_OK;
+    // vector path: rows of up to 16384 elements, everything 16-byte aligned
+    const bool aligned = E % 4 == 0 && E <= 16384 && ((uintptr_t)x & 15) == 0 && (!weight || ((uintptr_t)weight & 15) == 0) &&
+                         (!y || ((uintptr_t)y & 15) == 0) && (!add || (((uintptr_t)add & 15) == 0 && add_split_stride % 4 == 0));
+    if (aligned) {
+        int threads = ((E / 4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        const int iters = (E / 4 + threads - 1) / threads;
+#define LAUNCH_VEC(TA, TY, IT)                                                                                          \
+        add_rmsnorm_vec_kernel<TA, TY, IT><<<n_out, threads, 0, stream>>>(x, (const TA*)add, add_splits, add_split_stride, \
+                                                                          weight, eps, rows, E, (TY*)y, write_x)
+        PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, {
+            if (iters == 1) LAUNCH_VEC(TA, TY, 1); else if (iters == 2) LAUNCH_VEC(TA, TY, 2); else LAUNCH_VEC(TA, TY, 4);
+        }));
+#undef LAUNCH_VEC
+        return check_launch("add_rmsnorm");
+    }
     const size_t smem = (size_t)E * sizeof(float);
     if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "add_rmsnorm: width %d exceeds the supported 51200", E);
     constexpr int NT = 256;

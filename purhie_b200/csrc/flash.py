@@ -38,10 +38,10 @@ def _sms(device) -> int:
 
 
 def decode_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
-    """Splits of the key range so that about two CTAs per SM are busy; never more than there are key blocks."""
+    """Splits of the key range so that about four CTAs per SM are busy; never more than there are key blocks."""
     span = min(max_ctx, window) if window else max_ctx
     blocks = max(1, -(-span // BLOCK_KEYS))
-    want = max(1, (2 * sms) // max(1, n_rows * num_kv_heads))
+    want = max(1, (4 * sms) // max(1, n_rows * num_kv_heads))
     return max(1, min(want, blocks, MAX_SPLITS))
 
 

@@ -112,6 +112,93 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
     }
 }
 
+// Fast path for head_dim 128 rotated over its whole width in half pairs: one warp per (token, head), four
+// consecutive dimensions per lane, every load of the row in flight at once, the rotation partner (64 dimensions
+// away) fetched from lane ^ 16 by shuffle.  The order of the additions is the same for every launch shape.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TI, typename TQ, typename TKV>
+__global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits, long long split_stride,
+                                         const float* __restrict__ bias, const float* __restrict__ q_w,
+                                         const float* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
+                                         int max_pos, const int32_t* __restrict__ positions,
+                                         const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
+                                         TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
+                                         int page_size, int HQ, int HKV) {
+    constexpr int D = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * WARPS + warp;
+    const int t = blockIdx.x;
+    const int n_heads = HQ + 2 * HKV;
+    if (head >= n_heads) return;
+    const int d0 = lane * 4;
+    const TI* src = qkv + (size_t)t * n_heads * D + (size_t)head * D + d0;
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+        float4 u[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            u[j] = s0 + j < splits ? ld4(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (s0 + j < splits) { v.x += u[j].x; v.y += u[j].y; v.z += u[j].z; v.w += u[j].w; }
+    }
+    if (bias) {
+        const float4 b = ld4(bias + (size_t)head * D + d0);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
+    if (!is_q && !is_k) {
+        if (!slot_mapping) return;
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int h = head - HQ - HKV;
+        st4(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, v);
+        return;
+    }
+    const float* w = is_q ? q_w : k_w;
+    if (w) {
+        const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        const float4 g = ld4(w + d0);
+        v.x = v.x * inv * g.x; v.y = v.y * inv * g.y; v.z = v.z * inv * g.z; v.w = v.w * inv * g.w;
+    }
+    if (cos_sin) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+        const int j = (lane & 15) * 4;                       // pair index of this lane's first dimension
+        const float4 c = ld4(cos_sin + (size_t)pos * D + j), sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
+        float4 o;
+        o.x = __shfl_xor_sync(0xffffffffu, v.x, 16); o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
+        o.z = __shfl_xor_sync(0xffffffffu, v.z, 16); o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
+        if (lane < 16) {       // first half: a cos - b sin
+            v.x = v.x * c.x - o.x * sn.x; v.y = v.y * c.y - o.y * sn.y; v.z = v.z * c.z - o.z * sn.z; v.w = v.w * c.w - o.w * sn.w;
+        } else {               // second half: a sin + b cos (a is the partner)
+            v.x = o.x * sn.x + v.x * c.x; v.y = o.y * sn.y + v.y * c.y; v.z = o.z * sn.z + v.z * c.z; v.w = o.w * sn.w + v.w * c.w;
+        }
+    }
+    if (is_q) {
+        st4(q_out + ((size_t)t * HQ + head) * D + d0, v);
+    } else if (slot_mapping) {
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int h = head - HQ;
+        st4(k_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, v);
+    }
+}
+
 }  // namespace
 
 PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int splits, long long split_stride,
@@ -130,6 +217,18 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
         return fail(PH_ERR_ARG, "qk_norm_rope: a cache write needs the pool and its page size");
     if (T == 0) return PH_OK;
     dim3 grid(T, (HQ + 2 * HKV + WARPS - 1) / WARPS);
+    const bool fast = D == 128 && (!cos_sin || (n_rot == 128 && !interleaved)) && split_stride % 4 == 0 &&
+                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)bias |
+                        (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
+    if (fast) {
+#define LAUNCH_FAST(TI, TQ, TKV)                                                                                    \
+    qk_norm_rope_d128_kernel<TI, TQ, TKV><<<grid, WARPS * 32, 0, stream>>>(                                         \
+        (const TI*)qkv, splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,           \
+        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV)
+        PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_FAST(TI, TQ, TKV))));
+#undef LAUNCH_FAST
+        return check_launch("qk_norm_rope");
+    }
 #define LAUNCH(TI, TQ, TKV)                                                                                       \
     qk_norm_rope_kernel<TI, TQ, TKV><<<grid, WARPS * 32, 0, stream>>>(                                            \
         (const TI*)qkv, splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, n_rot, max_pos, positions,  \

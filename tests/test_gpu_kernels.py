@@ -345,3 +345,55 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
                 assert got.abs().max() < 4.0, (kernel, window, key_pos, ql)
             ref = dense_attention(case, HQ, HKV, D, window, scale)
             assert rel(out.cpu(), ref) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+# ---- per-head norm, rotation and cache write ---------------------------------------------------------------
+
+@pytest.mark.parametrize("HQ,HKV,D,n_rot,interleaved,splits,dtype", [
+    (4, 2, 16, 16, False, 1, torch.float32), (8, 2, 32, 32, False, 3, torch.float32), (3, 1, 48, 24, False, 1, torch.float32),
+    (6, 3, 64, 64, True, 1, torch.bfloat16), (32, 8, 128, 128, False, 1, torch.bfloat16),
+    (32, 8, 128, 128, False, 5, torch.bfloat16), (4, 4, 128, 64, False, 1, torch.bfloat16), (2, 1, 256, 256, False, 2, torch.float32)])
+def test_qk_norm_rope_kv_write(HQ, HKV, D, n_rot, interleaved, splits, dtype):
+    from purhie_b200.csrc import ops
+    T, ps, n_pages, max_pos, eps = 9, 8, 6, 64, 1e-5
+    width = (HQ + 2 * HKV) * D
+    in_dtype = torch.float32 if splits > 1 else dtype
+    qkv = rnd(splits, T, width, dtype=in_dtype, seed=1)
+    bias, qw, kw = rnd(width, seed=2) * 0.1, rnd(D, seed=3) * 0.2 + 1.0, rnd(D, seed=4) * 0.2 + 1.0
+    pos = torch.tensor([0, 1, 7, 8, 9, 31, 40, 62, 63], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([3, 47, 0, 8, 9, 17, 40, -1, 22], dtype=torch.int32, device=DEV)
+    half = n_rot // 2
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-2.0 * torch.arange(half, dtype=torch.float64) / n_rot))[None, :]
+    table = torch.cat([ang.cos(), ang.sin()], 1).float().to(DEV)
+    pool = torch.full((n_pages, 1, 2, HKV, ps, D), float("nan"), dtype=dtype, device=DEV)
+    q = torch.full((T, HQ, D), float("nan"), dtype=dtype, device=DEV)
+    ops.qk_norm_rope_kv_write(qkv, q, pos, num_heads=HQ, num_kv_heads=HKV, head_dim=D, eps=eps, q_norm=qw, k_norm=kw,
+                              bias=bias, cos_sin=table, n_rot=n_rot, slot_mapping=slots, k_base=pool[0, 0, 0],
+                              v_base=pool[0, 0, 1], page_stride=pool.stride(0), page_size=ps, splits=splits,
+                              interleaved=interleaved)
+    x = (qkv.double().sum(0) + bias.double()).cpu().view(T, HQ + 2 * HKV, D)
+    def norm_rot(v, w):
+        v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * w.double().cpu()
+        c, s = ang[pos.long().cpu()].cos()[:, None, :], ang[pos.long().cpu()].sin()[:, None, :]
+        out = v.clone()
+        if interleaved:
+            a, b = v[..., 0:n_rot:2], v[..., 1:n_rot:2]
+            out[..., 0:n_rot:2], out[..., 1:n_rot:2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = v[..., :half], v[..., half:n_rot]
+            out[..., :half], out[..., half:n_rot] = a * c - b * s, a * s + b * c
+        return out
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    assert rel(q.cpu(), norm_rot(x[:, :HQ], qw)) < tol
+    k_ref, v_ref = norm_rot(x[:, HQ:HQ + HKV], kw), x[:, HQ + HKV:]
+    written = torch.zeros(n_pages * ps, dtype=torch.bool)
+    for t in range(T):
+        sl = int(slots[t])
+        if sl < 0:
+            continue
+        written[sl] = True
+        assert rel(pool[sl // ps, 0, 0, :, sl % ps].cpu(), k_ref[t]) < tol
+        assert rel(pool[sl // ps, 0, 1, :, sl % ps].cpu(), v_ref[t]) < tol
+    # nothing but the mapped slots was touched
+    untouched = pool.float().cpu().permute(0, 4, 1, 2, 3, 5).reshape(n_pages * ps, -1)[~written]
+    assert torch.isnan(untouched).all()
