@@ -37,12 +37,28 @@ def _sms(device) -> int:
     return _sm_count[key]
 
 
+CTAS_PER_SM = 3            # decode CTAs that fit one SM (68 KB of shared memory each at head_dim 128)
+CTA_FIXED_COST = 4.0       # a CTA's start and end (query load, first block's latency, merge), in units of one block's time
+
+
 def decode_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
-    """Splits of the key range so that about four CTAs per SM are busy; never more than there are key blocks."""
+    """Splits of the key range.  CTAs run in waves of CTAS_PER_SM per SM; the number of splits is the one
+    that minimises waves x (fixed cost + blocks per split), so that neither a nearly empty last wave nor the
+    per-CTA overhead dominates."""
     span = min(max_ctx, window) if window else max_ctx
     blocks = max(1, -(-span // BLOCK_KEYS))
-    want = max(1, (4 * sms) // max(1, n_rows * num_kv_heads))
-    return max(1, min(want, blocks, MAX_SPLITS))
+    pairs = max(1, n_rows * num_kv_heads)
+    slots = CTAS_PER_SM * sms
+    best, best_cost = 1, None
+    for s in range(1, min(blocks, MAX_SPLITS) + 1):
+        per = -(-blocks // s)
+        if s > 1 and -(-blocks // per) != s:
+            continue                       # the same blocks per split as a smaller s: only empty CTAs more
+        waves = -(-(pairs * s) // slots)
+        cost = waves * (CTA_FIXED_COST + per)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def prefill(q, k_base, v_base, page_stride, page_size, block_table, seg_start, seg_ctx_len, tile_seg, tile_first,

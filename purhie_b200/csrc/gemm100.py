@@ -73,7 +73,11 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
 
 
 def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
-    """(swapped, block_n, splits) for a product of M tokens with an [N, K] weight."""
+    """(swapped, block_n, splits) for a product of M tokens with an [N, K] weight.
+
+    With few tokens the product is weight streaming: the work items (128-feature tile, split of K) should fill
+    whole waves of the SMs, so the number of splits is the one with the best wave efficiency (items / (waves *
+    SMs)), the fewest splits winning among near-equals, each split keeping at least four blocks of K."""
     kblocks = -(-K // BLOCK_K)
     if M >= 128:
         return False, (256 if N > 128 else 128 if N > 64 else 64), 1
@@ -83,8 +87,12 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     splits = 1
     if allow_split:
         a_tiles = -(-N // 128)
-        if a_tiles < sms:
-            splits = max(1, min(sms // a_tiles, kblocks // 4))
+        best = -1.0
+        for s in range(1, min(16, max(1, kblocks // 4)) + 1):
+            items = a_tiles * s
+            eff = items / (-(-items // sms) * sms)
+            if eff > best + 0.03:
+                best, splits = eff, s
     return True, block_n, splits
 
 
