@@ -5,7 +5,8 @@
 // depend on how many rows the launch has.
 //
 // Formulas (reference): RMSNorm y = x * rsqrt(mean(x^2) + eps) * w with the add fused in front
-// (src/gpu_ops.hip:24-56, 64-101); SwiGLU out = g / (1 + exp(-g)) * u (src/gpu_ops.hip:103-114);
+// (src/gpu_ops.hip:24-56, 64-101); SwiGLU out = g / (1 + exp(-g)) * u (src/gpu_ops.hip:103-114), here over
+// interleaved (gate, up) pairs;
 // embedding x[t] = table[token[t]] without scaling (src/qwen_model.cpp:1234-1244).
 #include "common.cuh"
 
@@ -128,20 +129,47 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
     }
 }
 
+// SwiGLU over rows laid out [g0, u0, g1, u1, ...] (gate and up rows of the weight interleaved, so that a tile of
+// the product holds matching pairs): out[t, j] = silu(g_j) * u_j.  Four outputs per thread when FF % 4 == 0.
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
                               int FF, long long total) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const long long t = idx / FF;
-    const int j = (int)(idx - t * FF);
-    const TI* g = gu + t * 2 * FF + j;
+    const TI* g = gu + idx * 2;
     float gv = 0.0f, uv = 0.0f;
     for (int s = 0; s < splits; ++s) {
         gv += to_float<TI>(g[(size_t)s * split_stride]);
-        uv += to_float<TI>(g[(size_t)s * split_stride + FF]);
+        uv += to_float<TI>(g[(size_t)s * split_stride + 1]);
     }
-    out[idx] = from_float<TO>(gv / (1.0f + expf(-gv)) * uv);
+    out[idx] = from_float<TO>(silu_mul(gv, uv));
+}
+
+template <typename TI, typename TO>
+__global__ void swiglu_vec_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
+                                  long long total4) {
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // group of four outputs
+    if (q >= total4) return;
+    const TI* src = gu + q * 8;
+    float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
+    for (int s0 = 0; s0 < splits; s0 += 2) {
+        float4 u[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const bool on = s0 + j < splits;
+            u[2 * j] = on ? Vec4<TI>::load(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            u[2 * j + 1] = on ? Vec4<TI>::load(src + (size_t)(s0 + j) * split_stride + 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (s0 + j < splits) {
+                a.x += u[2 * j].x; a.y += u[2 * j].y; a.z += u[2 * j].z; a.w += u[2 * j].w;
+                b.x += u[2 * j + 1].x; b.y += u[2 * j + 1].y; b.z += u[2 * j + 1].z; b.w += u[2 * j + 1].w;
+            }
+    }
+    Vec4<TO>::store(out + q * 4, make_float4(silu_mul(a.x, a.y), silu_mul(a.z, a.w), silu_mul(b.x, b.y), silu_mul(b.z, b.w)));
 }
 
 template <typename TI, typename TO>
@@ -206,6 +234,13 @@ PH_EXPORT int ph_swiglu(const void* gate_up, int in_dtype, int splits, long long
         return fail(PH_ERR_ARG, "swiglu: bad arguments (T %d, FF %d)", T, FF);
     const long long total = (long long)T * FF;
     if (total == 0) return PH_OK;
+    if (FF % 4 == 0 && split_stride % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        const long long total4 = total / 4;
+        const unsigned vblocks = (unsigned)((total4 + 255) / 256);
+        PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
+            swiglu_vec_kernel<TI, TO><<<vblocks, 256, 0, stream>>>((const TI*)gate_up, splits, split_stride, (TO*)out, total4)));
+        return check_launch("swiglu");
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
         swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)gate_up, splits, split_stride, (TO*)out, FF, total)));

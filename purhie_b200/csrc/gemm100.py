@@ -17,7 +17,7 @@ from .ops import KernelError, call, register_signatures
 
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_void_p, c_void_p],
+                             c_int, c_void_p, c_void_p],
 })
 
 BLOCK_K = 64
@@ -58,17 +58,19 @@ def sm_count(device) -> int:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, block_n: int, splits: int = 1,
-         max_ctas: int = 0) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1)."""
+         max_ctas: int = 0, swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1).  With
+    ``swiglu`` the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"gemm_tcgen05: {name} must be a contiguous bfloat16 CUDA tensor")
     N, K = w.shape
     M = x.numel() // K
-    if x.shape[-1] != K or out.numel() != splits * M * N or not out.is_contiguous():
+    if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         1 if swapped else 0, block_n, splits, max_ctas, error_flag(x.device).data_ptr(), ops._stream())
+         1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, error_flag(x.device).data_ptr(),
+         ops._stream())
     return out
 
 
@@ -96,10 +98,17 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     return True, block_n, splits
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool):
+def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool,
+           fuse_swiglu: bool = False):
+    """The product through the tcgen05 kernel.  ``fuse_swiglu`` (w holds (gate, up) row pairs): when the plain
+    orientation runs, the activation is applied in the epilogue and the result [M, N / 2] is marked activated."""
     from ..parts.base import Addend
     N, K = w.shape
     swapped, block_n, splits = plan(M, N, K, sm_count(x.device), allow_split)
+    if fuse_swiglu and not swapped and splits == 1 and N % 2 == 0:
+        out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
+        gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
+        return Addend(out, 1, activated=True)
     if splits > 1:
         out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)
     else:

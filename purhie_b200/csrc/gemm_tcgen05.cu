@@ -48,6 +48,7 @@ struct GemmParams {
     void* out;
     int out_bf16;        // 1: bfloat16 output, 0: float32
     int swapped;
+    int swiglu;          // 1: columns are (gate, up) pairs; out[a, j] = silu(D[a, 2j]) * D[a, 2j + 1] (plain orientation)
     long long ld;        // row length of out
     long long split_stride;
     int* error_flag;
@@ -277,7 +278,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
                 if (a < p.rows_a) {
-                    if (!p.swapped) {
+                    if (p.swiglu) {
+                        // the activation in the epilogue: the product itself never goes to memory
+                        const size_t base = (size_t)a * p.ld + (size_t)((b0 + c) >> 1);
+                        float h[CH / 2];
+#pragma unroll
+                        for (int j = 0; j < CH / 2; ++j) {
+                            const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+                            h[j] = g / (1.0f + __expf(-g)) * u;
+                        }
+                        const bool full_chunk = (b0 + c + CH <= p.rows_b);
+                        if (p.out_bf16) {
+                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
+                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                                for (int j = 0; j < CH / 2; j += 8) {
+                                    uint4 v;
+                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(h[j], h[j + 1]), h1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), h3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
+                                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
+                                    *(uint4*)(o + j) = v;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < CH / 2; ++j)
+                                    if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = __float2bfloat16_rn(h[j]);
+                            }
+                        } else {
+                            float* o = (float*)p.out + base;
+#pragma unroll
+                            for (int j = 0; j < CH / 2; ++j)
+                                if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = h[j];
+                        }
+                    } else if (!p.swapped) {
                         const size_t base = split_off + (size_t)a * p.ld + (size_t)(b0 + c);
                         const bool full_chunk = (b0 + c + CH <= p.rows_b);
                         if (p.out_bf16) {
@@ -419,8 +452,10 @@ PH_DEFINE_LAST_ERROR(ph_gemm100)
 
 // out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
 // side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).
+// swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue
+// (the formula of src/gpu_ops.hip:103-114 in the reference).
 PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                   int swapped, int block_n, int splits, int max_ctas, int* error_flag,
+                                   int swapped, int block_n, int splits, int max_ctas, int swiglu, int* error_flag,
                                    cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05: bad arguments (M %d, N %d, K %d)", M, N, K);
@@ -429,6 +464,8 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     const int kblocks = (K + BK - 1) / BK;
     if (splits < 1 || splits > kblocks) return fail(PH_ERR_ARG, "gemm_tcgen05: %d splits for %d blocks of K", splits, kblocks);
     if (splits > 1 && out_dtype != PH_F32) return fail(PH_ERR_ARG, "gemm_tcgen05: partial results are float32");
+    if (swiglu && (swapped || splits > 1 || (N & 1) || block_n < 32))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs the plain orientation, one split and an even N");
     const void* a = swapped ? w : x;
     const void* b = swapped ? x : w;
     const int rows_a = swapped ? N : M, rows_b = swapped ? M : N;
@@ -439,7 +476,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
     p.a_tiles = (rows_a + BM - 1) / BM; p.b_tiles = (rows_b + block_n - 1) / block_n;
     p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.ld = N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     switch (block_n) {
         case 16: return launch<16>(ma, mb, p, max_ctas, stream);

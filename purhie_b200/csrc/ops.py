@@ -145,7 +145,7 @@ def add_rmsnorm(x: torch.Tensor, add: Optional[torch.Tensor], weight: Optional[t
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, splits: int = 1) -> torch.Tensor:
-    """out[t, j] = silu(g[t, j]) * u[t, j] for gate_up rows laid out [gate (FF) | up (FF)]."""
+    """out[t, j] = silu(g[t, j]) * u[t, j] for gate_up rows laid out [g0, u0, g1, u1, ...]."""
     _need(gate_up, "gate_up"); _need(out, "out")
     FF = out.shape[-1]
     T = out.numel() // FF

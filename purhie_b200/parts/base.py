@@ -33,6 +33,7 @@ class Addend:
 
     tensor: torch.Tensor
     splits: int = 1
+    activated: bool = False      # a product whose activation was already applied in the kernel's epilogue
 
 
 class BuildContext:

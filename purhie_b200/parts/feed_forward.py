@@ -38,8 +38,10 @@ class SwiGLU(FeedForward):
         parts = [tensors[n["gate_proj"]], tensors[n["up_proj"]]]
         if parts[0].dtype != parts[1].dtype:
             parts = [t.float() for t in parts]
-        # [gate | up] rows in one matrix: one product, and the activation reads both halves of a row
-        self.gate_up_proj = Linear(torch.cat(parts, dim=0).contiguous(), "gate_up_proj", self._gemm)
+        # gate and up rows interleaved (g0, u0, g1, u1, ...) in one matrix: one product, and matching pairs sit
+        # side by side, so the activation can run in the product's epilogue (a layout choice only)
+        ff, e = parts[0].shape
+        self.gate_up_proj = Linear(torch.stack(parts, dim=1).reshape(2 * ff, e).contiguous(), "gate_up_proj", self._gemm)
         self.down_proj = Linear(tensors[n["down_proj"]], "down_proj", self._gemm)
 
     def required_libraries(self):
@@ -47,9 +49,12 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx) -> Addend:
         T, dt = ctx.T, self.compute_dtype
-        gu = self.gate_up_proj(x, ctx, "gate_up", dt, rows=T, allow_split=True)
-        act = ctx.workspace.get("ff_act", (T, self.intermediate_size), dt)
-        ops.swiglu(gu.tensor, act, splits=gu.splits)
+        gu = self.gate_up_proj(x, ctx, "gate_up", dt, rows=T, allow_split=True, fuse_swiglu=True)
+        if gu.activated:
+            act = gu.tensor
+        else:
+            act = ctx.workspace.get("ff_act", (T, self.intermediate_size), dt)
+            ops.swiglu(gu.tensor, act, splits=gu.splits)
         return self.down_proj(act, ctx, "ff_out", torch.float32, rows=T, allow_split=True)
 
 

@@ -41,7 +41,7 @@ class Linear:
         return ("core", "gemm100") if self._fast_kernel() else ("core",)
 
     def __call__(self, x: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, rows: Optional[int] = None,
-                 allow_split: bool = False) -> Addend:
+                 allow_split: bool = False, fuse_swiglu: bool = False) -> Addend:
         M = rows if rows is not None else x.shape[0]
         ws = ctx.workspace
         if self.weight.dtype == torch.float32 and x.dtype != torch.float32:
@@ -50,7 +50,7 @@ class Linear:
             x = x32
         fast = self._fast_kernel()
         if fast and x.dtype == torch.bfloat16:
-            return fast.linear(x, self.weight, ctx, out_name, out_dtype, M, allow_split)
+            return fast.linear(x, self.weight, ctx, out_name, out_dtype, M, allow_split, fuse_swiglu)
         out = ws.get(out_name, (M, self.out_features), out_dtype)
         ops.gemm_simple(x[:M], self.weight, out)
         return Addend(out, 1)

@@ -88,6 +88,19 @@ def test_gemm_tcgen05_against_the_plain_kernel_and_on_few_ctas():
     assert rel(a, b) < 2e-5 and torch.equal(a, c)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 512, 256), (300, 1000, 200), (2048, 2048, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_swiglu_epilogue(M, N, K, out_dtype):
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=9), rnd(N, K, dtype=torch.bfloat16, seed=10, scale=0.2)
+    out = torch.full((M, N // 2), float("nan"), dtype=out_dtype, device=DEV)
+    gemm100.gemm(x, w, out, swapped=False, block_n=256, swiglu=True)
+    gemm100.check_errors(DEV)
+    y = x.double() @ w.double().T
+    g, u = y[:, 0::2], y[:, 1::2]
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < (3e-5 if out_dtype == torch.float32 else 6e-3)
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     from purhie_b200.csrc import gemm100
     from purhie_b200.csrc.ops import KernelError
@@ -139,7 +152,7 @@ def test_swiglu(T, FF, splits):
         out = torch.empty(T, FF, dtype=dt, device=DEV)
         ops.swiglu(gu, out, splits=splits)
         s = gu.double().sum(0)
-        g, u = s[:, :FF], s[:, FF:]
+        g, u = s[:, 0::2], s[:, 1::2]                   # (gate, up) pairs side by side
         assert rel(out, g / (1 + torch.exp(-g)) * u) < tol
 
 
