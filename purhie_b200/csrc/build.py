@@ -43,6 +43,13 @@ LIBRARIES: Dict[str, dict] = {
         "flags": [],
         "link": [],
     },
+    # decode attention with its scratch in a fixed device array, for callers that cannot allocate
+    "decode_static": {
+        "sources": ["attention_decode_static.cu"],
+        "deps": ["attention_flash.cu", "attention_decode_static.h"],
+        "flags": [],
+        "link": [],
+    },
 }
 
 _HEADERS = ["common.cuh"]
@@ -126,7 +133,7 @@ def build_library(name: str, verbose: bool = True) -> str:
     spec = LIBRARIES[name]
     out_dir = build_dir()
     srcs = [os.path.join(CSRC, s) for s in spec["sources"]]
-    hdrs = [os.path.join(CSRC, h) for h in _HEADERS]
+    hdrs = [os.path.join(CSRC, h) for h in _HEADERS + spec.get("deps", [])]
     flags = ARCH_FLAGS + COMMON_FLAGS + spec["flags"]
     so = os.path.join(out_dir, f"libpurhie_{name}.so")
     stamp = so + ".stamp"
