@@ -34,7 +34,8 @@ LIBRARIES: Dict[str, dict] = {
         "link": [],
     },
     "flash": {
-        "sources": ["attention_flash.cu"],
+        "sources": ["attention_flash.cu", "attention_decode_bulk.cu"],
+        "deps": ["attention_mma.cuh", "mbarrier.cuh"],
         "flags": [],
         "link": [],
     },
@@ -46,7 +47,7 @@ LIBRARIES: Dict[str, dict] = {
     # decode attention with its scratch in a fixed device array, for callers that cannot allocate
     "decode_static": {
         "sources": ["attention_decode_static.cu"],
-        "deps": ["attention_flash.cu", "attention_decode_static.h"],
+        "deps": ["attention_flash.cu", "attention_decode_static.h", "attention_mma.cuh"],
         "flags": [],
         "link": [],
     },

@@ -16,6 +16,9 @@ from .ops import KernelError, call, register_signatures
 register_signatures("flash", {
     "ph_attention_prefill": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "ph_attention_decode_bulk": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_int, c_void_p, c_void_p],
     "ph_attention_decode": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                             c_void_p],
@@ -82,6 +85,63 @@ def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_r
          int(window or 0), float(scale), ops._stream())
 
 
+_flags = {}
+BULK_ERRORS = {111: "the attention producer waited too long for a free stage",
+               112: "an attention consumer waited too long for keys"}
+
+
+def error_flag(device) -> torch.Tensor:
+    key = torch.device(device)
+    if key not in _flags:
+        _flags[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _flags[key]
+
+
+def check_errors(device) -> None:
+    """Raise if the persistent decode kernel gave up on a wait since the last check (synchronises)."""
+    key = torch.device(device)
+    if key in _flags:
+        code = int(_flags[key].item())
+        if code:
+            _flags[key].zero_()
+            raise KernelError(f"attention_decode_bulk: {BULK_ERRORS.get(code, 'error')} (status {code})")
+
+
+def bulk_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
+    """Splits for the persistent kernel: one CTA per SM takes items in turn, so the time is (items per CTA,
+    rounded up) x (blocks per item + a small fixed cost); pick the split count that minimises it."""
+    span = min(max_ctx, window) if window else max_ctx
+    blocks = max(1, -(-span // BLOCK_KEYS))
+    pairs = max(1, n_rows * num_kv_heads)
+    best, best_cost = 1, None
+    for s in range(1, min(blocks, MAX_SPLITS) + 1):
+        per = -(-blocks // s)
+        if s > 1 and -(-blocks // per) != s:
+            continue
+        cost = -(-(pairs * s) // (2 * sms)) * (per + 0.5)         # two CTAs per SM
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
+def bulk_supports(page_size: int) -> bool:
+    return page_size % 8 == 0 and BLOCK_KEYS % page_size == 0
+
+
+def decode_bulk(q, k_base, v_base, page_stride, page_size, num_pages, block_table, row_list, n_rows, row_seg, positions, out,
+                workspace, *, num_heads, num_kv_heads, head_dim, window, scale, splits, max_ctas: int = 0) -> None:
+    """The persistent decode kernel fed by TMA copies of whole pages (attention_decode_bulk.cu)."""
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = workspace.get("attn_part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
+        part_ml = workspace.get("attn_part_ml", (n_rows, num_heads, splits, 2), torch.float32)
+    call("flash", "ph_attention_decode_bulk", q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), page_stride, page_size,
+         num_pages, block_table.data_ptr(), block_table.shape[-1], None if row_list is None else row_list.data_ptr(), n_rows,
+         row_seg.data_ptr(), positions.data_ptr(), None if part_o is None else part_o.data_ptr(),
+         None if part_ml is None else part_ml.data_ptr(), out.data_ptr(), num_heads, num_kv_heads, head_dim, splits,
+         int(window or 0), float(scale), max_ctas, error_flag(q.device).data_ptr(), ops._stream())
+
+
 def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
     """All rows of the step: q [T, HQ, D] bfloat16 -> out [T, HQ * D] bfloat16."""
     for name, t in (("q", q), ("out", out), ("k", cache.k_base)):
@@ -92,8 +152,14 @@ def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, w
                 ctx.seg_ctx_len, ctx.q_tile_seg, ctx.q_tile_first, ctx.n_q_tiles, out, num_heads=num_heads,
                 num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale)
     if ctx.n_decode_rows:
-        splits = ctx.extra.get("decode_splits") or decode_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx,
-                                                                _sms(q.device), window)
-        decode(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.decode_rows,
-               ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace, num_heads=num_heads,
-               num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale, splits=splits)
+        if ctx.extra.get("decode_kernel") == "cp_async" or not bulk_supports(cache.page_size) or not cache.num_pages:
+            splits = decode_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx, _sms(q.device), window)
+            decode(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.decode_rows,
+                   ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace, num_heads=num_heads,
+                   num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale, splits=splits)
+        else:
+            splits = bulk_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx, _sms(q.device), window)
+            decode_bulk(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages, group.block_table,
+                        ctx.decode_rows, ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace,
+                        num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale,
+                        splits=splits)

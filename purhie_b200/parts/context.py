@@ -65,6 +65,7 @@ class CacheView:
     v_base: Optional[torch.Tensor] = None   # page_stride elements apart
     page_stride: int = 0
     page_size: int = 0
+    num_pages: int = 0                      # pages of the pool the views belong to
     writable: bool = True                # False: another entry writes this cache, this one only reads
     state: Optional[torch.Tensor] = None    # [max_requests, *state_shape]
 

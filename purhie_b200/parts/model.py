@@ -107,7 +107,7 @@ class DecoderModel:
                 g = manager.groups[manager.entry_group[owner]]
                 slot = g.entry_slot(owner)
                 views.append(CacheView("pages", g.index, g.pool[0, slot, 0], g.pool[0, slot, 1], g.pool.stride(0),
-                                       manager.page_size, writable=(owner == i)))
+                                       manager.page_size, num_pages=g.pool.shape[0], writable=(owner == i)))
             elif need.kind == "state":
                 views.append(CacheView("state", state=manager.state[owner], writable=(owner == i)))
             else:

@@ -267,7 +267,7 @@ def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
     return out
 
 
-def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None):
+def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0):
     from purhie_b200.csrc import flash
     from purhie_b200.parts.context import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -286,11 +286,18 @@ def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None):
                       num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
     if dec_rows:
         max_ctx = max(c for c, ql in case["segs"] if ql == 1)
-        sp = splits or flash.decode_splits(len(dec_rows), HKV, max_ctx, 148, window)
-        flash.decode(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
-                     None if len(dec_rows) == case["T"] else i32(dec_rows), len(dec_rows), case["row_seg"],
-                     case["positions"], out, Workspace(DEV), num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window,
-                     scale=scale, splits=sp)
+        head = (case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size)
+        tail = (case["table"], None if len(dec_rows) == case["T"] else i32(dec_rows), len(dec_rows), case["row_seg"],
+                case["positions"], out, Workspace(DEV))
+        args = head + tail
+        kw = dict(num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
+        if bulk and flash.bulk_supports(page_size):
+            sp = splits or flash.bulk_splits(len(dec_rows), HKV, max_ctx, 148, window)
+            flash.decode_bulk(*head, case["pool"].shape[0], *tail, splits=sp, max_ctas=max_ctas, **kw)
+            flash.check_errors(DEV)
+        else:
+            sp = splits or flash.decode_splits(len(dec_rows), HKV, max_ctx, 148, window)
+            flash.decode(*args, splits=sp, **kw)
     return out
 
 
@@ -321,11 +328,17 @@ def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
     plain = run_generic(case, HQ, HKV, D, page_size, window, scale, torch.bfloat16)
     assert rel(out.cpu(), plain.cpu()) < 1e-2
     for sp in (1, 3, 32):                                  # any number of splits, more than there are blocks too
-        o2 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp)
-        assert rel(o2.cpu(), ref) < 1e-2
+        for bulk in (True, False):                         # the persistent bulk-copy kernel and the cp.async kernel
+            o2 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp, bulk=bulk)
+            assert not torch.isnan(o2.float()).any()
+            assert rel(o2.cpu(), ref) < 1e-2
+    # few CTAs: each walks many items, the stage ring and the query buffers wrap many times
+    for sp, ctas in ((2, 3), (2, 1), (3, 1), (1, 2)):
+        o3 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp, max_ctas=ctas)
+        assert rel(o3.cpu(), ref) < 1e-2, (sp, ctas)
 
 
-@pytest.mark.parametrize("kernel", ["generic32", "generic16", "flash"])
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "flash", "flash_cp_async"])
 def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
     """Random keys would hide a lost key among hundreds: make one key match the query so that it carries all the
     weight, then put it first in the context, on a page's edge, just inside and just outside the window."""
@@ -347,8 +360,8 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
             marker = torch.full((D,), 7.0, device=DEV)
             case["pool"][page, 0, 1, :, off] = marker.to(dtype)      # V[key_pos]
             v[key_pos] = marker.to(dtype)
-            if kernel == "flash":
-                out = run_flash(case, HQ, HKV, D, ps, window, scale)
+            if kernel.startswith("flash"):
+                out = run_flash(case, HQ, HKV, D, ps, window, scale, bulk=kernel == "flash")
             else:
                 out = run_generic(case, HQ, HKV, D, ps, window, scale, dtype)
             got = out[qrow].float().view(HQ, D)

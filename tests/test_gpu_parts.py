@@ -90,7 +90,7 @@ def test_attention_part_alone(dtype, window, HQ, HKV, D):
     need = att.cache_need()
     assert (need.kind, need.kv_heads, need.head_dim, need.window) == ("pages", HKV, D, window)
     pool = torch.full((16, 1, 2, HKV, ps, D), float("nan"), dtype=dtype, device=DEV)
-    view = CacheView("pages", 0, pool[0, 0, 0], pool[0, 0, 1], pool.stride(0), ps, True)
+    view = CacheView("pages", 0, pool[0, 0, 0], pool[0, 0, 1], pool.stride(0), ps, num_pages=16, writable=True)
     table = list(range(15, 15 - 9, -1))                       # pages in reverse order
     x = torch.randn(n1 + n2, E, generator=g)
     outs = []
