@@ -31,9 +31,7 @@ namespace mb = ph_mbar;
 
 constexpr int CONSUMER_WARPS = 4;
 constexpr int BULK_THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int STAGES = 2;            // two CTAs share an SM: 2 x 2 stages of 64 keys in flight
-constexpr int CTAS_PER_SM = 2;
-constexpr int PAGE_CACHE = 512;
+constexpr int PAGE_CACHE = 256;
 
 #define PH_ERR_WAIT_ATTN_PRODUCER 111
 #define PH_ERR_WAIT_ATTN_CONSUMER 112
@@ -95,75 +93,86 @@ template <int D> __device__ __forceinline__ uint32_t stage_off(int row, int chun
                       (row & (page_size - 1)) * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <int D>
-__global__ void __launch_bounds__(BULK_THREADS, CTAS_PER_SM)
+// Shared memory a CTA needs for G query heads per kv head and a ring of `stages` stages.
+__host__ __device__ constexpr int bulk_smem_bytes(int D, int G, int stages) {
+    return 1024 /* alignment */ + stages * 2 * BLOCK_KEYS * D * 2 + 2 * G * D * 2 + CONSUMER_WARPS * G * (D + 2) * 4 +
+           (2 * stages + 4) * 8 + PAGE_CACHE * 4;
+}
+
+template <int D, int STAGES, int CTAS>
+__global__ void __launch_bounds__(BULK_THREADS, CTAS)
 attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const BulkParams p) {
     constexpr int HALVES = D / 64;
     constexpr int TILE = BLOCK_KEYS * D * 2;              // bytes of K (or of V) for 64 keys
     constexpr int QROW = D * 2;
     constexpr int RS = D + 2;
+    const int G = p.HQ / p.HKV;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* kv = smem;                             // [STAGES][K tile, V tile], 1024-byte aligned
-    unsigned char* q_tiles = kv + STAGES * 2 * TILE;      // [2][16 rows x D], rows >= G stay zero
-    float* red = (float*)(q_tiles + 2 * 16 * QROW);       // [4 warps][16][D + 2]
-    uint64_t* full = (uint64_t*)(red + CONSUMER_WARPS * 16 * RS);
+    unsigned char* kv = smem;                             // [STAGES][page blocks of K and V], 1024-byte aligned
+    unsigned char* q_tiles = kv + STAGES * 2 * TILE;      // [2][G rows x D]
+    float* red = (float*)(q_tiles + 2 * G * QROW);        // [4 warps][G][D + 2]
+    uint64_t* full = (uint64_t*)(red + CONSUMER_WARPS * G * RS);
     uint64_t* empty = full + STAGES;
     uint64_t* q_full = empty + STAGES;
     uint64_t* q_empty = q_full + 2;
     int32_t* pages = (int32_t*)(q_empty + 2);             // [PAGE_CACHE] the producer's copy of the item's block table
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = p.HQ / p.HKV;
     const int work_total = p.n_rows * p.HKV * p.splits;
-    for (int i = threadIdx.x; i < 2 * 16 * QROW / 16; i += BULK_THREADS) ((uint4*)q_tiles)[i] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mb::init(&full[s], 1); mb::init(&empty[s], CONSUMER_WARPS); }
         for (int s = 0; s < 2; ++s) { mb::init(&q_full[s], 1); mb::init(&q_empty[s], CONSUMER_WARPS); }
         mb::fence_init();
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeroed query rows, before bulk copies land beside them
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
         // ---- producer ----
-        // Lane 0 runs the pipeline (waits, expected bytes, copies); the other lanes only help to fetch the item's
-        // page numbers.  The warp meets at two points per item and nowhere else, so lanes cannot get out of step.
+        // All lanes run the same control flow: lane 0 waits on the barriers and announces the bytes, lane j
+        // issues the box of the stage's page j.  The box coordinates of the whole item are worked out by all lanes
+        // at once when the item starts, so that a stage costs the producer a few instructions.
         int stage = 0, qi = 0;
         uint32_t phase = 0, q_phase = 0;
         int ok = 1;
-        const int pages_per_block = BLOCK_KEYS / p.page_size;
-        for (int w = blockIdx.x; w < work_total; w += gridDim.x) {
-            ok = __shfl_sync(0xffffffffu, ok, 0);          // (A) everyone is done with the previous item
-            if (!ok) break;
+        const int psh = p.page_shift, ppb = BLOCK_KEYS >> psh;              // pages per stage
+        const int page_block = 2 * HALVES * p.page_size * 128;             // bytes of one page's box
+        for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
             const Item it = make_item(p, w);
             const int32_t* table = p.block_table + (size_t)p.row_seg[it.t] * p.table_stride;
-            // the pages this item touches, fetched once instead of once per box
-            const int first_page = (it.lo_page + it.b_first * BLOCK_KEYS) / p.page_size;
-            const int last_key = min(it.z, it.lo_page + (it.b_last + 1) * BLOCK_KEYS - 1);
-            const int n_pages = it.b_first <= it.b_last ? last_key / p.page_size - first_page + 1 : 0;
-            for (int j = lane; j < n_pages && j < PAGE_CACHE; j += 32) pages[j] = table[first_page + j];
-            __syncwarp();                                  // (B) the page numbers are in shared memory
-            if (lane != 0) continue;
+            const int nb = it.b_last - it.b_first + 1;
+            const int key_first = it.lo_page + it.b_first * BLOCK_KEYS;
+            // row coordinate of page j of the item: its place in the pool, or out of range (zeros) past the token
+            auto page_row = [&](int j) {
+                const int pos = key_first + (j << psh);
+                if (pos > it.z) return p.total_rows;
+                return (int)((long long)table[pos >> psh] * p.rows_per_page + (long long)it.g * p.page_size);
+            };
+            __syncwarp();                                                    // the previous item's boxes are issued
+            for (int j = lane; j < nb * ppb && j < PAGE_CACHE; j += 32) pages[j] = page_row(j);
+            __syncwarp();
             // the query rows of this kv head's group are contiguous: one copy
-            if (!mb::wait(&q_empty[qi], q_phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER)) { ok = 0; continue; }
-            mb::arrive_expect_tx(&q_full[qi], G * QROW);
-            mb::bulk_copy(q_tiles + qi * 16 * QROW, p.q + ((size_t)it.t * p.HQ + (size_t)it.g * G) * D, G * QROW, &q_full[qi]);
+            if (lane == 0) {
+                ok = mb::wait(&q_empty[qi], q_phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER) ? 1 : 0;
+                if (ok) {
+                    mb::arrive_expect_tx(&q_full[qi], G * QROW);
+                    mb::bulk_copy(q_tiles + qi * G * QROW, p.q + ((size_t)it.t * p.HQ + (size_t)it.g * G) * D, G * QROW, &q_full[qi]);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             if (++qi == 2) { qi = 0; q_phase ^= 1; }
-            for (int b = it.b_first; b <= it.b_last; ++b) {
-                if (!mb::wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER)) { ok = 0; break; }
-                mb::arrive_expect_tx(&full[stage], 2 * TILE);
-                unsigned char* base = kv + stage * 2 * TILE;
-                const int key0 = it.lo_page + b * BLOCK_KEYS;
-                for (int pj = 0; pj < pages_per_block; ++pj) {
-                    const int pos = key0 + pj * p.page_size;
-                    int row = p.total_rows;                 // out of range: the boxes are filled with zeros
-                    if (pos <= it.z) {
-                        const int pi = pos / p.page_size - first_page;
-                        const int page = pi < PAGE_CACHE ? pages[pi] : table[first_page + pi];
-                        row = (int)((long long)page * p.rows_per_page + (long long)it.g * p.page_size);
-                    }
-                    tma_load_page(base + pj * (2 * HALVES * p.page_size * 128), &map_kv, &full[stage], row);
+            for (int b = 0; b < nb; ++b) {
+                if (lane == 0) {
+                    ok = mb::wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER) ? 1 : 0;
+                    if (ok) mb::arrive_expect_tx(&full[stage], 2 * TILE);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);                        // also: the stage is free for every lane
+                if (!ok) break;
+                if (lane < ppb) {
+                    const int j = b * ppb + lane;
+                    const int row = j < PAGE_CACHE ? pages[j] : page_row(j);
+                    tma_load_page(kv + stage * 2 * TILE + lane * page_block, &map_kv, &full[stage], row);
                 }
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -185,16 +194,62 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
         uint32_t phase = 0, q_phase = 0;
         bool ok = true;
         const int r0 = lane >> 2, r1 = r0 + 8;
-        float* mine = red + (size_t)warp * 16 * RS;
+        const int ps = p.page_size, psh = p.page_shift;
+        float* mine = red + (size_t)warp * G * RS;
+
+        // S = Q K^T over this warp's 16 keys of a stage; even and odd steps of D accumulate apart, so that four
+        // chains of dependent instructions run instead of two.
+        auto qk = [&](uint32_t st, const uint32_t (&qf)[D / 16][4], float (&s)[2][4]) {
+            float s2[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { s[nt][i] = 0.0f; s2[nt][i] = 0.0f; }
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t b0, b1, b2, b3;
+                const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+                const int chunk = ks * 2 + ((lane >> 3) & 1);
+                ldmatrix_x4(st + stage_off<D>(row, chunk, 0, ps, psh), b0, b1, b2, b3);
+                if (ks & 1) {
+                    mma_bf16(s2[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                    mma_bf16(s2[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                } else {
+                    mma_bf16(s[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                    mma_bf16(s[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[nt][i] += s2[nt][i];
+        };
+        // O += P V over the same 16 keys
+        auto pv = [&](uint32_t st, const float (&s)[2][4], float (&o)[D / 8][4]) {
+            const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+            const uint32_t a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int dt = 0; dt < D / 8; dt += 2) {
+                uint32_t b0, b1, b2, b3;
+                const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                ldmatrix_x4_trans(st + stage_off<D>(row, dt + (lane >> 4), 1, ps, psh), b0, b1, b2, b3);
+                mma_bf16(o[dt], a0, a1, a2, a3, b0, b1);
+                mma_bf16(o[dt + 1], a0, a1, a2, a3, b2, b3);
+            }
+        };
+
         for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
             const Item it = make_item(p, w);
             uint32_t qf[D / 16][4];
             if (!mb::wait(&q_full[qi], q_phase, p.error_flag, PH_ERR_WAIT_ATTN_CONSUMER)) { ok = false; break; }
-            const uint32_t q_tile = smem_u32(q_tiles + qi * 16 * QROW);
+            {   // the tile's rows beyond the group repeat a real row; their results are never stored
+                const uint32_t q_tile = smem_u32(q_tiles + qi * G * QROW);
+                const int qrow = min(lane & 15, G - 1);
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks)             // plain rows: read once per item, bank conflicts do not matter
-                ldmatrix_x4(q_tile + (lane & 15) * QROW + (ks * 2 + (lane >> 4)) * 16, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
-            const int q_used = qi;                          // released after the item's last block, see below
+                for (int ks = 0; ks < D / 16; ++ks)
+                    ldmatrix_x4(q_tile + qrow * QROW + (ks * 2 + (lane >> 4)) * 16, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+            }
+            const int q_used = qi;                          // given back after the item's last block, see below
             if (++qi == 2) { qi = 0; q_phase ^= 1; }
 
             float o[D / 8][4];
@@ -203,13 +258,34 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
             for (int dt = 0; dt < D / 8; ++dt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) o[dt][i] = 0.0f;
-            for (int b = it.b_first; b <= it.b_last; ++b) {
+
+            // The scores of block j + 1 are computed in the same straight-line code as the softmax and P V of
+            // block j, so that the scheduler can overlap the two dependency chains.
+            const int nb = it.b_last - it.b_first + 1;
+            float s_cur[2][4];
+            if (nb > 0) {
                 if (!mb::wait(&full[stage], phase, p.error_flag, PH_ERR_WAIT_ATTN_CONSUMER)) { ok = false; break; }
+                qk(smem_u32(kv + stage * 2 * TILE), qf, s_cur);
+            }
+            for (int j = 0; j < nb; ++j) {
                 unsigned char* st_ptr = kv + stage * 2 * TILE;
                 const uint32_t st = smem_u32(st_ptr);
-                const int ps = p.page_size, psh = p.page_shift;
-                const int key0 = it.lo_page + b * BLOCK_KEYS + warp * 16;
-                if (key0 <= it.z) {
+                const int key0 = it.lo_page + (it.b_first + j) * BLOCK_KEYS + warp * 16;
+                int nstage = stage + 1;
+                uint32_t nphase = phase;
+                if (nstage == STAGES) { nstage = 0; nphase ^= 1; }
+                if (j + 1 < nb) {
+                    if (!mb::wait(&full[nstage], nphase, p.error_flag, PH_ERR_WAIT_ATTN_CONSUMER)) { ok = false; break; }
+                    float s_next[2][4];
+                    qk(smem_u32(kv + nstage * 2 * TILE), qf, s_next);
+                    // not the item's last block: every key is at or before the token; only the window's start masks
+                    softmax_update<D, 16>(s_cur, key0, it.z, it.z, it.lo, it.lo, true, p.scale_log2, m, l, o);
+                    pv(st, s_cur, o);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s_cur[nt][i] = s_next[nt][i];
+                } else if (key0 <= it.z) {
                     const bool tail = key0 + 15 > it.z;
                     if (tail) {
                         // value rows after the token's position inside its page may hold anything: zero this warp's
@@ -219,51 +295,14 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
                         }
                         __syncwarp();
                     }
-                    float s[2][4];
-                    {   // S = Q K^T over this warp's 16 keys; even and odd steps of D accumulate apart, so that
-                        // four chains of dependent instructions run instead of two
-                        float s2[2][4];
-#pragma unroll
-                        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) { s[nt][i] = 0.0f; s2[nt][i] = 0.0f; }
-#pragma unroll
-                        for (int ks = 0; ks < D / 16; ++ks) {
-                            uint32_t b0, b1, b2, b3;
-                            const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-                            const int chunk = ks * 2 + ((lane >> 3) & 1);
-                            ldmatrix_x4(st + stage_off<D>(row, chunk, 0, ps, psh), b0, b1, b2, b3);
-                            if (ks & 1) {
-                                mma_bf16(s2[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-                                mma_bf16(s2[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
-                            } else {
-                                mma_bf16(s[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-                                mma_bf16(s[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
-                            }
-                        }
-#pragma unroll
-                        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) s[nt][i] += s2[nt][i];
-                    }
-                    softmax_update<D, 16>(s, key0, it.z, it.z, it.lo, it.lo, tail || key0 < it.lo, p.scale_log2, m, l, o);
-                    {   // O += P V
-                        const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
-                        const uint32_t a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
-#pragma unroll
-                        for (int dt = 0; dt < D / 8; dt += 2) {
-                            uint32_t b0, b1, b2, b3;
-                            const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                            ldmatrix_x4_trans(st + stage_off<D>(row, dt + (lane >> 4), 1, ps, psh), b0, b1, b2, b3);
-                            mma_bf16(o[dt], a0, a1, a2, a3, b0, b1);
-                            mma_bf16(o[dt + 1], a0, a1, a2, a3, b2, b3);
-                        }
-                    }
+                    softmax_update<D, 16>(s_cur, key0, it.z, it.z, it.lo, it.lo, true, p.scale_log2, m, l, o);
+                    pv(st, s_cur, o);
                     if (tail) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our zeros, before the next copy lands there
                 }
                 __syncwarp();
                 if (lane == 0) mb::arrive(&empty[stage]);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                stage = nstage;
+                phase = nphase;
             }
             if (!ok) break;
             // The query buffer is given back only now: the compiler is free to fetch the fragments again from
@@ -271,28 +310,28 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
             // while the item runs.
             __syncwarp();
             if (lane == 0) mb::arrive(&q_empty[q_used]);
-            // merge the four warps (each saw different keys); rows >= G are padding
+            // merge the four warps (each saw different keys); fragment rows >= G are padding
 #pragma unroll
             for (int dt = 0; dt < D / 8; ++dt) {
                 const int d = dt * 8 + (lane & 3) * 2;
-                mine[r0 * RS + d] = o[dt][0]; mine[r0 * RS + d + 1] = o[dt][1];
-                mine[r1 * RS + d] = o[dt][2]; mine[r1 * RS + d + 1] = o[dt][3];
+                if (r0 < G) { mine[r0 * RS + d] = o[dt][0]; mine[r0 * RS + d + 1] = o[dt][1]; }
+                if (r1 < G) { mine[r1 * RS + d] = o[dt][2]; mine[r1 * RS + d + 1] = o[dt][3]; }
             }
             if ((lane & 3) == 0) {
-                mine[r0 * RS + D] = m[0]; mine[r0 * RS + D + 1] = l[0];
-                mine[r1 * RS + D] = m[1]; mine[r1 * RS + D + 1] = l[1];
+                if (r0 < G) { mine[r0 * RS + D] = m[0]; mine[r0 * RS + D + 1] = l[0]; }
+                if (r1 < G) { mine[r1 * RS + D] = m[1]; mine[r1 * RS + D + 1] = l[1]; }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
             for (int idx = threadIdx.x; idx < G * D; idx += CONSUMER_WARPS * 32) {
                 const int r = idx / D, d = idx % D;
                 float mm = -INFINITY;
 #pragma unroll
-                for (int ww = 0; ww < CONSUMER_WARPS; ++ww) mm = fmaxf(mm, red[((size_t)ww * 16 + r) * RS + D]);
+                for (int ww = 0; ww < CONSUMER_WARPS; ++ww) mm = fmaxf(mm, red[((size_t)ww * G + r) * RS + D]);
                 const float use = mm == -INFINITY ? 0.0f : mm;
                 float acc = 0.0f, ll = 0.0f;
 #pragma unroll
                 for (int ww = 0; ww < CONSUMER_WARPS; ++ww) {
-                    const float* src = red + ((size_t)ww * 16 + r) * RS;
+                    const float* src = red + ((size_t)ww * G + r) * RS;
                     const float c = exp2f(src[D] - use);
                     acc += c * src[d];
                     ll += c * src[D + 1];
@@ -385,25 +424,36 @@ bool make_page_map(CUtensorMap* out, const void* k_base, long long kv_stride_byt
     return true;
 }
 
-template <int D> int launch_bulk(const CUtensorMap& mkv, const BulkParams& p, int max_ctas, cudaStream_t stream) {
-    constexpr int BYTES = 1024 + STAGES * 2 * BLOCK_KEYS * D * 2 + 2 * 16 * D * 2 + CONSUMER_WARPS * 16 * (D + 2) * 4 +
-                          (2 * STAGES + 4) * 8 + PAGE_CACHE * 4;
-    static bool configured = false;
-    auto kernel = attention_decode_bulk_kernel<D>;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BYTES) != cudaSuccess)
-            return fail(PH_ERR_LAUNCH, "attention_decode_bulk: cannot reserve %d bytes of shared memory", BYTES);
-        configured = true;
+template <int D, int STAGES, int CTAS>
+int launch_config(const CUtensorMap& mkv, const BulkParams& p, int bytes, int max_ctas, cudaStream_t stream) {
+    static int configured = 0;
+    auto kernel = attention_decode_bulk_kernel<D, STAGES, CTAS>;
+    if (configured < bytes) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+            return fail(PH_ERR_LAUNCH, "attention_decode_bulk: cannot reserve %d bytes of shared memory", bytes);
+        configured = bytes;
     }
     const int work = p.n_rows * p.HKV * p.splits;
-    int grid = CTAS_PER_SM * sm_count();
+    int grid = CTAS * sm_count();
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
-    kernel<<<grid, BULK_THREADS, BYTES, stream>>>(mkv, p);
+    kernel<<<grid, BULK_THREADS, bytes, stream>>>(mkv, p);
     if (p.splits > 1)
         attention_combine_bulk_kernel<D><<<dim3(p.n_rows, p.HQ), D < 128 ? D : 128, 0, stream>>>(
             p.part_o, p.part_ml, p.row_list, p.out, p.HQ, p.splits);
     return check_launch("attention_decode_bulk");
+}
+
+// Two CTAs per SM with three stages each when that fits the SM's shared memory, else two stages each, else one
+// CTA with four stages: what counts is warps per SM (the consumers wait on dependent tensor-core instructions)
+// and enough copies in flight.
+template <int D> int launch_bulk(const CUtensorMap& mkv, const BulkParams& p, int max_ctas, cudaStream_t stream) {
+    const int G = p.HQ / p.HKV;
+    constexpr int SM_BYTES = 227 * 1024;
+    const int b3 = bulk_smem_bytes(D, G, 3), b2 = bulk_smem_bytes(D, G, 2), b4 = bulk_smem_bytes(D, G, 4);
+    if (2 * (b3 + 1024) <= SM_BYTES) return launch_config<D, 3, 2>(mkv, p, b3, max_ctas, stream);
+    if (2 * (b2 + 1024) <= SM_BYTES) return launch_config<D, 2, 2>(mkv, p, b2, max_ctas, stream);
+    return launch_config<D, 4, 1>(mkv, p, b4, max_ctas, stream);
 }
 
 }  // namespace
