@@ -90,9 +90,10 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     if allow_split:
         a_tiles = -(-N // 128)
         best = -1.0
+        slots = sms * (2 if block_n <= 64 else 1)          # the kernel runs two CTAs per SM for small tiles
         for s in range(1, min(16, max(1, kblocks // 4)) + 1):
             items = a_tiles * s
-            eff = items / (-(-items // sms) * sms)
+            eff = items / (-(-items // slots) * slots)
             if eff > best + 0.03:
                 best, splits = eff, s
     return True, block_n, splits

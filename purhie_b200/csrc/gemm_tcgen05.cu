@@ -161,16 +161,20 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Few tokens (BN <= 64: weight streaming): two CTAs share an SM, each with half the stages, so that one CTA's
+// start-up and epilogue overlap the other's streaming.  Many tokens: one CTA per SM with all the stages.
 template <int BN> struct TileConfig {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 10 ? 10 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : 2 * BN;          // a power of two: BN is one
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
 template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, TileConfig<BN>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     using Cfg = TileConfig<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -439,7 +443,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
         configured = true;
     }
     const int work = p.a_tiles * p.b_tiles * p.splits;
-    int grid = sm_count();
+    int grid = Cfg::CTAS_PER_SM * sm_count();
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
     kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
