@@ -125,7 +125,9 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
         for (int s = 0; s < 2; ++s) { mb::init(&q_full[s], 1); mb::init(&q_empty[s], CONSUMER_WARPS); }
         mb::fence_init();
     }
+    pdl_launch_dependents();
     __syncthreads();
+    pdl_wait();                       // the queries and this step's keys and values come from the kernel before
 
     if (warp == CONSUMER_WARPS) {
         // ---- producer ----
@@ -353,6 +355,8 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
 template <int D>
 __global__ void attention_combine_bulk_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int32_t* __restrict__ row_list, __nv_bfloat16* __restrict__ out, int HQ, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x, h = blockIdx.y;
     const int t = row_list ? row_list[i] : i;
     const size_t slot0 = ((size_t)i * HQ + h) * splits;
@@ -437,10 +441,10 @@ int launch_config(const CUtensorMap& mkv, const BulkParams& p, int bytes, int ma
     int grid = CTAS * sm_count();
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
-    kernel<<<grid, BULK_THREADS, bytes, stream>>>(mkv, p);
+    launch_overlapped(kernel, dim3(grid), dim3(BULK_THREADS), (size_t)bytes, stream, mkv, p);
     if (p.splits > 1)
-        attention_combine_bulk_kernel<D><<<dim3(p.n_rows, p.HQ), D < 128 ? D : 128, 0, stream>>>(
-            p.part_o, p.part_ml, p.row_list, p.out, p.HQ, p.splits);
+        launch_overlapped(attention_combine_bulk_kernel<D>, dim3(p.n_rows, p.HQ), dim3(D < 128 ? D : 128), 0, stream,
+                          (const float*)p.part_o, (const float*)p.part_ml, p.row_list, p.out, p.HQ, p.splits);
     return check_launch("attention_decode_bulk");
 }
 

@@ -8,6 +8,9 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <utility>
 
 #define PH_OK 0
 #define PH_ERR_ARG 1
@@ -41,6 +44,40 @@ inline int check_launch(const char* what) {
 }
 
 inline bool valid_dtype(int d) { return d == PH_F32 || d == PH_BF16; }
+
+// Programmatic dependent launch.  A kernel launched through launch_overlapped may start while the kernel
+// before it in the stream is still running: its blocks become resident as soon as every block of that kernel has
+// called pdl_launch_dependents() (or exited), run whatever does not depend on that kernel's results (set-up,
+// prefetch of weights), and stop at pdl_wait() until that kernel has completed and its writes are visible.  Every
+// such kernel calls pdl_wait() before it reads anything a predecessor produced and before it writes global
+// memory at all.  PURHIE_PDL=0 in the environment turns the attribute off (the device calls are then no-ops).
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PURHIE_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }

@@ -17,6 +17,8 @@ using namespace ph;
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int32_t* __restrict__ ids,
                                     float* __restrict__ out, int E, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);       // ids are validated on the host; never read outside
@@ -81,6 +83,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
                                        const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * E;
@@ -150,6 +154,8 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int splits, long long s
 template <typename TI, typename TO>
 __global__ void swiglu_vec_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
                                   long long total4) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;      // group of four outputs
     if (q >= total4) return;
     const TI* src = gu + q * 8;
@@ -185,7 +191,8 @@ PH_EXPORT int ph_embed_gather(const void* table, int table_dtype, const int32_t*
     if (!table || !ids || !out || T < 0 || E < 1 || V < 1 || !valid_dtype(table_dtype))
         return fail(PH_ERR_ARG, "embed_gather: bad arguments (T %d, E %d, V %d, dtype %d)", T, E, V, table_dtype);
     if (T == 0) return PH_OK;
-    PH_DISPATCH(table_dtype, TT, embed_gather_kernel<TT><<<T, 256, 0, stream>>>((const TT*)table, ids, out, E, V));
+    PH_DISPATCH(table_dtype, TT, launch_overlapped(embed_gather_kernel<TT>, dim3(T), dim3(256), 0, stream, (const TT*)table,
+                                                   ids, out, E, V));
     return check_launch("embed_gather");
 }
 
@@ -205,8 +212,8 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
         if (threads > 1024) threads = 1024;
         const int iters = (E / 4 + threads - 1) / threads;
 #define LAUNCH_VEC(TA, TY, IT)                                                                                          \
-        add_rmsnorm_vec_kernel<TA, TY, IT><<<n_out, threads, 0, stream>>>(x, (const TA*)add, add_splits, add_split_stride, \
-                                                                          weight, eps, rows, E, (TY*)y, write_x)
+        launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT>, dim3(n_out), dim3(threads), 0, stream, x, (const TA*)add,   \
+                          add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x)
         PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, {
             if (iters == 1) LAUNCH_VEC(TA, TY, 1); else if (iters == 2) LAUNCH_VEC(TA, TY, 2); else LAUNCH_VEC(TA, TY, 4);
         }));
@@ -238,7 +245,8 @@ PH_EXPORT int ph_swiglu(const void* gate_up, int in_dtype, int splits, long long
         const long long total4 = total / 4;
         const unsigned vblocks = (unsigned)((total4 + 255) / 256);
         PH_DISPATCH(in_dtype, TI, PH_DISPATCH(out_dtype, TO,
-            swiglu_vec_kernel<TI, TO><<<vblocks, 256, 0, stream>>>((const TI*)gate_up, splits, split_stride, (TO*)out, total4)));
+            launch_overlapped(swiglu_vec_kernel<TI, TO>, dim3(vblocks), dim3(256), 0, stream, (const TI*)gate_up, splits,
+                              split_stride, (TO*)out, total4)));
         return check_launch("swiglu");
     }
     const unsigned blocks = (unsigned)((total + 255) / 256);

@@ -206,23 +206,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int work_total = p.a_tiles * p.b_tiles * p.splits;
 
+    pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
-                const int split = w % p.splits, tile = w / p.splits;
-                const int a0 = (tile % p.a_tiles) * BM, b0 = (tile / p.a_tiles) * BN;
-                const int kb0 = (int)((long long)p.kblocks * split / p.splits);
-                const int kb1 = (int)((long long)p.kblocks * (split + 1) / p.splits);
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-                    tma_load_2d(smem_a + stage * A_BYTES, &map_a, &full[stage], kb * BK, a0);
-                    tma_load_2d(smem_b + stage * Cfg::B_BYTES, &map_b, &full[stage], kb * BK, b0);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            // The walk over (work item, block of K) as an iterator, so that the weight tiles of the first stages
+            // can be requested before the kernel in front of this one has finished: weights do not depend on it,
+            // activations do.
+            struct Walk {
+                const GemmParams& p;
+                int w, kb, kb1, a0, b0;
+                bool valid;
+                __device__ void start(int w_, int work_total) {
+                    w = w_;
+                    valid = w < work_total;
+                    if (!valid) return;
+                    const int split = w % p.splits, tile = w / p.splits;
+                    a0 = (tile % p.a_tiles) * BM;
+                    b0 = (tile / p.a_tiles) * BN;
+                    kb = (int)((long long)p.kblocks * split / p.splits);
+                    kb1 = (int)((long long)p.kblocks * (split + 1) / p.splits);
                 }
+                __device__ void next(int stride, int work_total) { if (++kb == kb1) start(w + stride, work_total); }
+            };
+            Walk wa{p}, wb{p};
+            wa.start(blockIdx.x, work_total);
+            wb.start(blockIdx.x, work_total);
+            int pre = 0;
+            if (p.swapped) {
+                // A is the weight: fill the (still empty) ring with weight tiles now
+                for (; pre < STAGES && wa.valid; ++pre) {
+                    mbar_arrive_expect_tx(&full[pre], Cfg::STAGE_BYTES);
+                    tma_load_2d(smem_a + pre * A_BYTES, &map_a, &full[pre], wa.kb * BK, wa.a0);
+                    wa.next(gridDim.x, work_total);
+                }
+            }
+            pdl_wait();
+            for (int s = 0; s < pre; ++s) {                  // the activation tiles of those stages
+                tma_load_2d(smem_b + s * Cfg::B_BYTES, &map_b, &full[s], wb.kb * BK, wb.b0);
+                wb.next(gridDim.x, work_total);
+            }
+            int stage = pre == STAGES ? 0 : pre;
+            uint32_t phase = pre == STAGES ? 1 : 0;
+            bool ok = true;
+            while (wa.valid) {
+                if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) { ok = false; break; }
+                mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+                tma_load_2d(smem_a + stage * A_BYTES, &map_a, &full[stage], wa.kb * BK, wa.a0);
+                tma_load_2d(smem_b + stage * Cfg::B_BYTES, &map_b, &full[stage], wa.kb * BK, wa.b0);
+                wa.next(gridDim.x, work_total);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
             // Do not leave while copies may still be in flight: wait until the consumer released every stage.
             for (int s = 0; s < STAGES && ok; ++s) {
@@ -264,6 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else {
         const int q = warp & 3;                        // the TMEM lane quarter this warp may read
+        pdl_wait();                                    // nothing is written before the kernels in front are done
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -446,7 +479,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     int grid = Cfg::CTAS_PER_SM * sm_count();
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
-    kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, p);
+    launch_overlapped(kernel, dim3(grid), dim3(NUM_THREADS), (size_t)Cfg::SMEM_BYTES, stream, ma, mb, p);
     return check_launch("gemm_tcgen05");
 }
 

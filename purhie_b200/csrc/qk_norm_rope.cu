@@ -138,6 +138,8 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
                                          TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
                                          int page_size, int HQ, int HKV) {
     constexpr int D = 128;
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * WARPS + warp;
     const int t = blockIdx.x;
@@ -222,9 +224,9 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
                         (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
     if (fast) {
 #define LAUNCH_FAST(TI, TQ, TKV)                                                                                    \
-    qk_norm_rope_d128_kernel<TI, TQ, TKV><<<grid, WARPS * 32, 0, stream>>>(                                         \
-        (const TI*)qkv, splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,           \
-        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV)
+    launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV>, grid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, splits,   \
+                      split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions, slot_mapping, (TQ*)q_out, \
+                      (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV)
         PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_FAST(TI, TQ, TKV))));
 #undef LAUNCH_FAST
         return check_launch("qk_norm_rope");
