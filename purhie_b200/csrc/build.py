@@ -34,7 +34,7 @@ LIBRARIES: Dict[str, dict] = {
         "link": [],
     },
     "flash": {
-        "sources": ["attention_flash.cu", "attention_decode_bulk.cu"],
+        "sources": ["attention_flash.cu", "attention_decode_bulk.cu", "attention_prefill_tc5.cu"],
         "deps": ["attention_mma.cuh", "mbarrier.cuh"],
         "flags": [],
         "link": [],

@@ -19,6 +19,9 @@ register_signatures("flash", {
     "ph_attention_decode_bulk": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_int, c_void_p, c_void_p],
+    "ph_attention_prefill_tc5": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                 c_void_p, c_void_p],
     "ph_attention_decode": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                             c_void_p],
@@ -72,6 +75,19 @@ def prefill(q, k_base, v_base, page_stride, page_size, block_table, seg_start, s
          ops._stream())
 
 
+def tc5_supports(head_dim: int, page_size: int) -> bool:
+    return head_dim == 128 and page_size in (8, 16)
+
+
+def prefill_tc5(q, n_rows, k_base, v_base, page_stride, page_size, num_pages, block_table, seg_start, seg_ctx_len, tile_seg,
+                tile_first, n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+    """The tcgen05 prefill kernel (attention_prefill_tc5.cu); tiles of 128 rows."""
+    call("flash", "ph_attention_prefill_tc5", q.data_ptr(), n_rows, k_base.data_ptr(), v_base.data_ptr(), page_stride,
+         page_size, num_pages, block_table.data_ptr(), block_table.shape[-1], seg_start.data_ptr(), seg_ctx_len.data_ptr(),
+         tile_seg.data_ptr(), tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim,
+         int(window or 0), float(scale), error_flag(q.device).data_ptr(), ops._stream())
+
+
 def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_rows, row_seg, positions, out, workspace, *,
            num_heads, num_kv_heads, head_dim, window, scale, splits) -> None:
     part_o = part_ml = None
@@ -87,7 +103,9 @@ def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_r
 
 _flags = {}
 BULK_ERRORS = {111: "the attention producer waited too long for a free stage",
-               112: "an attention consumer waited too long for keys"}
+               112: "an attention consumer waited too long for keys",
+               121: "the prefill attention producer waited too long", 122: "the prefill attention tensor-core warp waited too long",
+               123: "a prefill attention softmax warp waited too long"}
 
 
 def error_flag(device) -> torch.Tensor:
@@ -104,7 +122,7 @@ def check_errors(device) -> None:
         code = int(_flags[key].item())
         if code:
             _flags[key].zero_()
-            raise KernelError(f"attention_decode_bulk: {BULK_ERRORS.get(code, 'error')} (status {code})")
+            raise KernelError(f"attention kernel: {BULK_ERRORS.get(code, 'error')} (status {code})")
 
 
 def bulk_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
@@ -147,7 +165,13 @@ def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, w
     for name, t in (("q", q), ("out", out), ("k", cache.k_base)):
         if t.dtype != torch.bfloat16:
             raise KernelError(f"attention_flash: {name} must be bfloat16")
-    if ctx.n_q_tiles:
+    if ctx.n_q_tiles and ctx.n_q_tiles_large and tc5_supports(head_dim, cache.page_size) and cache.num_pages \
+            and ctx.extra.get("prefill_kernel") != "mma_sync":
+        prefill_tc5(q, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
+                    group.block_table, ctx.seg_start, ctx.seg_ctx_len, ctx.q_tile_large_seg, ctx.q_tile_large_first,
+                    ctx.n_q_tiles_large, out, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                    window=window, scale=scale)
+    elif ctx.n_q_tiles:
         prefill(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.seg_start,
                 ctx.seg_ctx_len, ctx.q_tile_seg, ctx.q_tile_first, ctx.n_q_tiles, out, num_heads=num_heads,
                 num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale)

@@ -18,7 +18,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages, OutOfSlots
 from ..config.base import ModelConfig, load_config, lookup_architecture
-from ..parts.context import Q_TILE, GroupStep, StepContext, Workspace
+from ..parts.context import Q_TILE, Q_TILE_LARGE, GroupStep, StepContext, Workspace
 from ..parts.model import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -69,6 +69,7 @@ class _Layout:
     n_decode: int
     n_tiles: int
     decode_max_ctx: int
+    n_tiles_large: int = 0
 
 
 @dataclass
@@ -200,7 +201,7 @@ class Engine:
             slots.append(cache.slot_of(e.request_id))
             want.extend(base + int(w) for w in e.want)
         T, S = len(tokens), len(entries)
-        decode_rows, tile_seg, tile_first, decode_max_ctx = [], [], [], 0
+        decode_rows, tile_seg, tile_first, decode_max_ctx, big_seg, big_first = [], [], [], 0, [], []
         for s, n in enumerate(q_lens):
             if n == 1:
                 decode_rows.append(seg_start[s])
@@ -209,12 +210,16 @@ class Engine:
                 for first in range(0, n, Q_TILE):
                     tile_seg.append(s)
                     tile_first.append(first)
+                for first in range(0, n, Q_TILE_LARGE):
+                    big_seg.append(s)
+                    big_first.append(first)
         widths = []
         for g in cache.groups:
             w = max(len(cache.block_table(e.request_id, g.index)) for e in entries)
             widths.append(max(table_width or 0, -(-w // 8) * 8))
         sizes = [T, T, T, S + 1, S, S, max(len(want), 1)] + [S * w for w in widths] + [T] * len(cache.groups) + \
-                [max(len(decode_rows), 1), max(len(tile_seg), 1), max(len(tile_seg), 1)]
+                [max(len(decode_rows), 1), max(len(tile_seg), 1), max(len(tile_seg), 1), max(len(big_seg), 1),
+                 max(len(big_seg), 1)]
         flat: List[int] = []
         flat += tokens + positions + row_seg + seg_start + ctx_lens + slots + (want if want else [0])
         for g, w in zip(cache.groups, widths):
@@ -224,9 +229,9 @@ class Engine:
         for g in cache.groups:
             for e in entries:
                 flat += cache.token_slots(e.request_id, g.index, cache.length(e.request_id), len(e.tokens))
-        flat += (decode_rows or [0]) + (tile_seg or [0]) + (tile_first or [0])
+        flat += (decode_rows or [0]) + (tile_seg or [0]) + (tile_first or [0]) + (big_seg or [0]) + (big_first or [0])
         return _Layout(flat, sizes, T, S, widths, q_lens, ctx_lens, len(want), len(decode_rows), len(tile_seg),
-                       decode_max_ctx)
+                       decode_max_ctx, len(big_seg))
 
     def _upload(self, flat: List[int], dev: torch.Tensor) -> None:
         """One copy of the metadata to the device, through two pinned buffers used in turn: a buffer is
@@ -258,7 +263,8 @@ class Engine:
                           groups=groups, workspace=workspace, compute_dtype=self.dtype, decode_only=lay.n_tiles == 0,
                           decode_rows=None if lay.n_tiles == 0 else parts[7 + 2 * G], n_decode_rows=lay.n_decode,
                           decode_max_ctx=lay.decode_max_ctx, q_tile_seg=parts[8 + 2 * G],
-                          q_tile_first=parts[9 + 2 * G], n_q_tiles=lay.n_tiles)
+                          q_tile_first=parts[9 + 2 * G], n_q_tiles=lay.n_tiles, q_tile_large_seg=parts[10 + 2 * G],
+                          q_tile_large_first=parts[11 + 2 * G], n_q_tiles_large=lay.n_tiles_large)
         return ctx, parts[6]
 
     def build_context(self, entries: Sequence[StepEntry]):

@@ -14,7 +14,8 @@ import torch
 from .base import Addend
 
 
-Q_TILE = 64        # rows of a query tile of the prefill attention kernel
+Q_TILE = 64        # rows of a query tile of the mma.sync prefill attention kernel
+Q_TILE_LARGE = 128 # rows of a query tile of the tcgen05 prefill attention kernel
 
 
 class Workspace:
@@ -94,6 +95,10 @@ class StepContext:
     q_tile_seg: Optional[torch.Tensor] = None
     q_tile_first: Optional[torch.Tensor] = None
     n_q_tiles: int = 0
+    # the same segments cut into tiles of Q_TILE_LARGE rows (the tcgen05 prefill kernel)
+    q_tile_large_seg: Optional[torch.Tensor] = None
+    q_tile_large_first: Optional[torch.Tensor] = None
+    n_q_tiles_large: int = 0
     extra: dict = field(default_factory=dict)
 
     @property

@@ -267,7 +267,7 @@ def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
     return out
 
 
-def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0):
+def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True):
     from purhie_b200.csrc import flash
     from purhie_b200.parts.context import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -280,7 +280,14 @@ def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True
                 tile_seg.append(s); tile_first.append(f)
         start += ql
     i32 = lambda x: torch.tensor(x or [0], dtype=torch.int32, device=DEV)
-    if tile_seg:
+    if tile_seg and tc5 and flash.tc5_supports(D, page_size):
+        big = [(s, f) for s, (ctx, ql) in enumerate(case["segs"]) if ql > 1 for f in range(0, ql, 128)]
+        flash.prefill_tc5(case["q"], case["T"], case["k_base"], case["v_base"], case["page_stride"], page_size,
+                          case["pool"].shape[0], case["table"], case["seg_start"], case["seg_ctx"], i32([b[0] for b in big]),
+                          i32([b[1] for b in big]), len(big), out, num_heads=HQ, num_kv_heads=HKV, head_dim=D,
+                          window=window, scale=scale)
+        flash.check_errors(DEV)
+    elif tile_seg:
         flash.prefill(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
                       case["seg_start"], case["seg_ctx"], i32(tile_seg), i32(tile_first), len(tile_seg), out,
                       num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=window, scale=scale)
@@ -315,7 +322,7 @@ def test_attention_generic(HQ, HKV, D, page_size, window, dtype):
 
 @pytest.mark.parametrize("HQ,HKV,D,page_size,window", [
     (8, 2, 128, 16, None), (4, 4, 64, 16, None), (6, 2, 64, 8, 40), (16, 1, 128, 64, 200), (32, 8, 128, 16, None),
-    (2, 1, 128, 3, 65)])
+    (2, 1, 128, 3, 65), (4, 2, 128, 8, 150), (3, 3, 128, 16, 77)])
 def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
     # portions that start mid-page, cross many blocks, end inside a tile; decode rows short and long
     segs = [(1, 1), (64, 64), (200, 130), (300, 1), (65, 2), (700, 1), (513, 257), (63, 1), (128, 1)]
@@ -327,6 +334,8 @@ def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
     assert rel(out.cpu(), ref) < 1e-2
     plain = run_generic(case, HQ, HKV, D, page_size, window, scale, torch.bfloat16)
     assert rel(out.cpu(), plain.cpu()) < 1e-2
+    legacy = run_flash(case, HQ, HKV, D, page_size, window, scale, tc5=False)      # the mma.sync prefill kernel
+    assert rel(legacy.cpu(), ref) < 1e-2
     for sp in (1, 3, 32):                                  # any number of splits, more than there are blocks too
         for bulk in (True, False):                         # the persistent bulk-copy kernel and the cp.async kernel
             o2 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp, bulk=bulk)
