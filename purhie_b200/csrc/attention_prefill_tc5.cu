@@ -1,17 +1,20 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05), keys and values straight from cache pages.
 //
-// One CTA per (128 query tokens of one request, query head); two CTAs share an SM, so that while one waits for
-// its softmax the other keeps the tensor pipe busy.  Roles inside a CTA:
-//   warp 0    TMA producer: the query tile once (3-D box), then per block of 64 keys the pages' keys and values
-//             (one box per page and 64-element half, 128-byte swizzled), two blocks in flight;
-//   warp 1    issues tcgen05.mma from one lane: S = Q K^T (M 128, N 64, K 128) into tensor memory, and after
-//             the softmax O += P V (M 128, N 128, K 64) with V read as an MN-major operand; O stays in tensor
-//             memory for the whole tile;
+// One CTA per (128 query tokens of one request, query head); two CTAs share an SM.  Roles inside a CTA:
+//   warp 0    TMA producer: the query tile once (4-D box), then per block of 64 keys the pages' keys and values
+//             (one box per page and 64-element half, 128-byte swizzled).  K and V have rings of their own: a K
+//             tile is free once its S is done, a V tile once P V has read it.
+//   warp 1    issues tcgen05.mma from one lane: S = Q K^T (M 128, N 64, K 128) into one of two score buffers in
+//             tensor memory, and O += P V (M 128, N 128, K 64) with P read from tensor memory and V as an
+//             MN-major operand from shared memory; O stays in tensor memory for the whole tile.  S of block b + 1
+//             is issued before P V of block b, so the softmax never waits for its scores.
 //   warps 2-5 softmax: thread i owns query row i.  It reads its row of S with tcgen05.ld (no shuffles: the row is
-//             in one thread), masks, keeps the running maximum and sum in float32 and writes P as bfloat16 over
-//             the block's K tile (no longer needed once S is done) in the swizzled K-major layout the tensor
-//             core reads.  The exponent's reference maximum only moves when the row maximum has grown by more
-//             than 2^8 since it was set; then the row of O in tensor memory is rescaled (tcgen05.ld / st).
+//             in one thread), masks only in blocks at the diagonal or the window's edge, keeps the running
+//             maximum and sum in float32 (packed two-element float32 instructions, ex2.approx) and writes P as
+//             bfloat16 pairs back over its scores with tcgen05.st.  The exponent's reference maximum only moves
+//             when the row maximum has grown by more than 2^8 since it was set; then the row of O in tensor
+//             memory is rescaled (tcgen05.ld / st).
+// Tensor memory: columns 0-63 scores (then P) of even blocks, 64-191 O, 192-255 scores of odd blocks.
 // A row at absolute position z sees positions max(0, z - window + 1) .. z.  Pages past the tile's last token
 // come from an out-of-range coordinate (zeros), scores of invisible keys are replaced by -inf and value rows
 // after the last token inside its page are zeroed before P V, so unwritten page slots may hold anything.
@@ -41,7 +44,7 @@ constexpr int HALF_Q = BM * 128;        // bytes of one 64-element half of the Q
 constexpr int HALF_KV = BN * 128;       // bytes of one half of a K or V block
 constexpr int Q_BYTES = 2 * HALF_Q;
 constexpr int KV_BYTES = 2 * HALF_KV;   // K (or V) of one block
-constexpr int TMEM_COLS = 256;          // S: columns 0-63, O_blk: columns 64-191
+constexpr int TMEM_COLS = 256;          // S of even blocks: columns 0-63, O: 64-191, S of odd blocks: 192-255
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + KV_STAGES * 2 * KV_BYTES + 256;
 constexpr float RESCALE_STEP = 8.0f;    // log2 units the row maximum may outgrow the reference before O is rescaled
 constexpr float LOG2E = 1.4426950408889634f;
@@ -142,19 +145,57 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// 2^x, one instruction; -inf gives 0.
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two float32 operations in one instruction.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n.reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n.reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\n"
+        "add.rn.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
+// A operand from tensor memory: 128 rows on the lanes, 16 bfloat16 of K in 8 columns.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const Tc5Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = smem;                                   // [half][128 rows][128 B]
-    unsigned char* kv = q_tile + Q_BYTES;                           // [stage][K: half, key, 128 B | V: half, key, 128 B]
-    uint64_t* bars = (uint64_t*)(kv + KV_STAGES * 2 * KV_BYTES);
+    unsigned char* k_ring = q_tile + Q_BYTES;                       // [stage][half][key][128 B]
+    unsigned char* v_ring = k_ring + KV_STAGES * KV_BYTES;          // [stage][half][key][128 B]
+    uint64_t* bars = (uint64_t*)(v_ring + KV_STAGES * KV_BYTES);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;                 // [KV_STAGES] keys and values of a block have landed
-    uint64_t* kv_empty = kv_full + KV_STAGES;     // [KV_STAGES] ... and have been read
-    uint64_t* s_full = kv_empty + KV_STAGES;      // S of a block is in tensor memory
-    uint64_t* p_full = s_full + 1;                // P of a block is in shared memory, O is rescaled
+    uint64_t* k_full = bars + 1;                  // [KV_STAGES] keys of a block have landed
+    uint64_t* k_empty = k_full + KV_STAGES;       // [KV_STAGES] ... and the tile may be loaded again
+    uint64_t* v_full = k_empty + KV_STAGES;       // [KV_STAGES] values of a block have landed
+    uint64_t* v_empty = v_full + KV_STAGES;       // [KV_STAGES] ... and have been read
+    uint64_t* s_full = v_empty + KV_STAGES;       // [2] S of a block is in tensor memory (two buffers in turn)
+    uint64_t* p_full = s_full + 2;                // P of a block is written, O is rescaled
     uint64_t* o_full = p_full + 1;                // P V of a block has been added to O
     uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
 
@@ -173,8 +214,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 
     if (threadIdx.x == 0) {
         mb::init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) { mb::init(&kv_full[s], 1); mb::init(&kv_empty[s], 1); }
-        mb::init(s_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mb::init(&k_full[s], 1); mb::init(&k_empty[s], 1);
+            mb::init(&v_full[s], 1); mb::init(&v_empty[s], 1);
+        }
+        mb::init(&s_full[0], 1);
+        mb::init(&s_full[1], 1);
         mb::init(p_full, 4);
         mb::init(o_full, 1);
         mb::fence_init();
@@ -189,10 +234,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     tc_fence_after();
     pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 64;
+    const uint32_t tmem_o = tmem_base + 64;
+    auto tmem_s = [&](int b) { return tmem_base + ((b & 1) ? 192u : 0u); };
+    // block b uses stage b % KV_STAGES for the (b / KV_STAGES)-th time
+    auto stage_of = [](int b) { return b % KV_STAGES; };
+    auto use_parity = [](int b) { return (uint32_t)((b / KV_STAGES) & 1); };
 
     if (warp == 0) {
-        // ---- producer ----
+        // ---- producer: K of block b, then V of block b - 1: the order in which their tiles come free ----
         const int32_t* table = p.block_table + (size_t)seg * p.table_stride;
         const int psh = p.page_shift, ppb = BN >> psh;
         int ok = 1;
@@ -200,30 +249,34 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             mb::arrive_expect_tx(q_full, Q_BYTES);
             tma_load_4d(q_tile, &map_q, q_full, 0, row0 + first, 0, h);       // box {64, 128 rows, 2 halves, 1 head}
         }
-        int stage = 0;
-        uint32_t phase = 0;
-        for (int b = 0; b < n_blocks; ++b) {
+        auto load = [&](int b, bool is_v) {
+            const int stage = stage_of(b);
+            uint64_t* full = is_v ? &v_full[stage] : &k_full[stage];
             if (lane == 0) {
-                ok = mb::wait(&kv_empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_TC5_PRODUCER) ? 1 : 0;
-                if (ok) mb::arrive_expect_tx(&kv_full[stage], 2 * KV_BYTES);
+                ok = mb::wait(is_v ? &v_empty[stage] : &k_empty[stage], use_parity(b) ^ 1, p.error_flag, PH_ERR_WAIT_TC5_PRODUCER) ? 1 : 0;
+                if (ok) mb::arrive_expect_tx(full, KV_BYTES);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            // lane (page j, half, K or V) issues one box
-            if (lane < ppb * 4) {
-                const int pj = lane >> 2, half = (lane >> 1) & 1, is_v = lane & 1;
+            if (!ok) return;
+            // lane (page j, half) issues one box
+            if (lane < ppb * 2) {
+                const int pj = lane >> 1, half = lane & 1;
                 const int pos = lo_page + b * BN + (pj << psh);
                 int row = p.total_rows;                       // past the tile's last token: zeros
                 if (pos <= z_last) row = (int)((long long)table[pos >> psh] * p.rows_per_page + (long long)g * p.page_size);
-                unsigned char* dst = kv + stage * 2 * KV_BYTES + is_v * KV_BYTES + half * HALF_KV + (pj << psh) * 128;
-                tma_load_2d(dst, is_v ? &map_v : &map_k, &kv_full[stage], half * 64, row);
+                unsigned char* dst = (is_v ? v_ring : k_ring) + stage * KV_BYTES + half * HALF_KV + (pj << psh) * 128;
+                tma_load_2d(dst, is_v ? &map_v : &map_k, full, half * 64, row);
             }
-            if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
+        };
+        for (int b = 0; b <= n_blocks && ok; ++b) {
+            if (b < n_blocks) load(b, false);
+            if (b > 0 && ok) load(b - 1, true);
         }
         if (lane == 0 && ok) {
-            for (int s = 0; s < KV_STAGES; ++s) {      // no copy may be in flight when the CTA ends
-                if (!mb::wait(&kv_empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_TC5_PRODUCER)) break;
-                if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
+            // no copy may be in flight when the CTA ends: the last blocks' tiles have been read
+            for (int b = max(0, n_blocks - KV_STAGES); b < n_blocks; ++b) {
+                if (!mb::wait(&k_empty[stage_of(b)], use_parity(b), p.error_flag, PH_ERR_WAIT_TC5_PRODUCER)) break;
+                if (!mb::wait(&v_empty[stage_of(b)], use_parity(b), p.error_flag, PH_ERR_WAIT_TC5_PRODUCER)) break;
             }
         }
     } else if (warp == 1) {
@@ -232,33 +285,49 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             constexpr uint32_t idesc_s = make_idesc(BM, BN, 0);      // S = Q K^T: both K-major
             constexpr uint32_t idesc_o = make_idesc(BM, D, 1);       // O += P V: V is MN-major
             bool ok = mb::wait(q_full, 0, p.error_flag, PH_ERR_WAIT_TC5_MMA);
-            int stage = 0;
-            uint32_t phase = 0, ph_blk = 0;
-            for (int b = 0; b < n_blocks && ok; ++b) {
-                if (!mb::wait(&kv_full[stage], phase, p.error_flag, PH_ERR_WAIT_TC5_MMA)) { ok = false; break; }
-                // S of the previous block was read before its P was announced, which the previous turn waited for
-                tc_fence_after();
-                const uint32_t k_tile = smem_u32(kv + stage * 2 * KV_BYTES), v_tile = k_tile + KV_BYTES;
+            // S of block b + 1 is issued before P V of block b where its keys have landed, so that the softmax of
+            // the next block finds its scores ready while the tensor core adds this block to O.  Its buffer in
+            // tensor memory held S (and P) of block b - 1, whose P V was issued before: the pipe keeps the order.
+            auto issue_s = [&](int b) {
+                const uint32_t k_tile = smem_u32(k_ring + stage_of(b) * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * HALF_Q + (ks & 3) * 32, offk = (ks >> 2) * HALF_KV + (ks & 3) * 32;
-                    umma_bf16(tmem_s, make_desc(smem_u32(q_tile) + off, 16, 1024), make_desc(k_tile + offk, 16, 1024), idesc_s,
+                    umma_bf16(tmem_s(b), make_desc(smem_u32(q_tile) + off, 16, 1024), make_desc(k_tile + offk, 16, 1024), idesc_s,
                               ks > 0 ? 1u : 0u);
                 }
-                umma_commit(s_full);
-                // P now lies where K was
-                if (!mb::wait(p_full, ph_blk, p.error_flag, PH_ERR_WAIT_TC5_MMA)) { ok = false; break; }
+                umma_commit(&s_full[b & 1]);
+                umma_commit(&k_empty[stage_of(b)]);      // the keys are not needed again
+            };
+            if (ok && n_blocks > 0) {
+                ok = mb::wait(&k_full[0], 0, p.error_flag, PH_ERR_WAIT_TC5_MMA);
+                if (ok) { tc_fence_after(); issue_s(0); }
+            }
+            for (int b = 0; b < n_blocks && ok; ++b) {
+                const int stage = stage_of(b);
+                bool next_issued = b + 1 >= n_blocks;
+                if (!next_issued && mb::test_wait(&k_full[stage_of(b + 1)], use_parity(b + 1))) {
+                    tc_fence_after();
+                    issue_s(b + 1);
+                    next_issued = true;
+                }
+                if (!mb::wait(p_full, b & 1, p.error_flag, PH_ERR_WAIT_TC5_MMA)) { ok = false; break; }
+                if (!mb::wait(&v_full[stage], use_parity(b), p.error_flag, PH_ERR_WAIT_TC5_MMA)) { ok = false; break; }
                 tc_fence_after();
+                const uint32_t v_tile = smem_u32(v_ring + stage * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
-                    // A: 16 keys further along P's 128-byte rows; B: 16 keys = two groups of 8 rows further down V
-                    umma_bf16(tmem_o, make_desc(k_tile + ks * 32, 16, 1024), make_desc(v_tile + ks * 2048, HALF_KV, 1024), idesc_o,
-                              (b > 0 || ks > 0) ? 1u : 0u);
+                    // A: 16 keys = 8 columns further in tensor memory; B: 16 keys = two groups of 8 rows further down V
+                    umma_bf16_ts(tmem_o, tmem_s(b) + ks * 8, make_desc(v_tile + ks * 2048, HALF_KV, 1024), idesc_o,
+                                 (b > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(o_full);
-                umma_commit(&kv_empty[stage]);          // P and V of this block have been read
-                if (++stage == KV_STAGES) { stage = 0; phase ^= 1; }
-                ph_blk ^= 1;
+                umma_commit(&v_empty[stage]);
+                if (!next_issued) {
+                    if (!mb::wait(&k_full[stage_of(b + 1)], use_parity(b + 1), p.error_flag, PH_ERR_WAIT_TC5_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_s(b + 1);
+                }
             }
         }
     } else {
@@ -270,44 +339,63 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         float m_ref = -INFINITY;                         // the maximum the exponents refer to
         float l = 0.0f;
-        uint32_t ph_blk = 0;
         bool ok = true;
         for (int b = 0; b < n_blocks && ok; ++b) {
             const int key0 = lo_page + b * BN;
-            const int stage = b % KV_STAGES;
-            unsigned char* k_tile = kv + stage * 2 * KV_BYTES;
-            if (!mb::wait(s_full, ph_blk, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
+            const int stage = stage_of(b);
+            if (!mb::wait(&s_full[b & 1], (b >> 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
             tc_fence_after();
-            float s[BN];
+            // the row's 64 scores, as pairs
+            float2 s[BN / 2];
             {
-                uint32_t raw[32];
-                tmem_ld32(tmem_s + lane_addr, raw);
+                uint32_t raw[BN];
+                tmem_ld32(tmem_s(b) + lane_addr, raw);
+                tmem_ld32(tmem_s(b) + lane_addr + 32, raw + 32);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) s[j] = __uint_as_float(raw[j]);
-                tmem_ld32(tmem_s + lane_addr + 32, raw);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s[32 + j] = __uint_as_float(raw[j]);
+                for (int j = 0; j < BN / 2; ++j) s[j] = make_float2(__uint_as_float(raw[2 * j]), __uint_as_float(raw[2 * j + 1]));
             }
-            const bool need_mask = key0 + BN - 1 > z || key0 < lo;
-            float mx = -INFINITY;
+            if (key0 + BN - 1 > z || key0 < lo) {            // only the blocks at the diagonal and at the window's edge
 #pragma unroll
-            for (int j = 0; j < BN; ++j) {
-                float v = s[j] * p.scale_log2;
-                if (need_mask && (key0 + j > z || key0 + j < lo)) v = -INFINITY;
-                s[j] = v;
-                mx = fmaxf(mx, v);
+                for (int j = 0; j < BN / 2; ++j) {
+                    if (key0 + 2 * j > z || key0 + 2 * j < lo) s[j].x = -INFINITY;
+                    if (key0 + 2 * j + 1 > z || key0 + 2 * j + 1 < lo) s[j].y = -INFINITY;
+                }
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < BN / 2; j += 2) {
+                mx0 = fmaxf(mx0, fmaxf(s[j].x, s[j].y));
+                mx1 = fmaxf(mx1, fmaxf(s[j + 1].x, s[j + 1].y));
+            }
+            const float mx = fmaxf(mx0, mx1) * p.scale_log2;       // the scale is positive: the maximum commutes with it
             // move the reference only when the maximum has outgrown it by more than RESCALE_STEP
             float corr = 1.0f;
             if (mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY)) {
-                corr = exp2f(m_ref - mx);                 // 0 the first time
+                corr = ex2(m_ref - mx);                   // 0 the first time
                 m_ref = mx;
             }
-            // O of the blocks so far must be complete before it is rescaled
+            // P = 2^(s * scale - reference) as bfloat16 pairs over the first 32 columns of this block's scores
+            const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg_ref, neg_ref);
+            float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+            uint32_t packed[BN / 2];
+#pragma unroll
+            for (int j = 0; j < BN / 2; j += 2) {
+                const float2 a0 = fma2(s[j], scale2, neg2), a1 = fma2(s[j + 1], scale2, neg2);
+                const float2 e0 = make_float2(ex2(a0.x), ex2(a0.y)), e1 = make_float2(ex2(a1.x), ex2(a1.y));
+                sum_a = add2(sum_a, e0);
+                sum_b = add2(sum_b, e1);
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(e0.x, e0.y), h1 = __floats2bfloat162_rn(e1.x, e1.y);
+                packed[j] = *(uint32_t*)&h0;
+                packed[j + 1] = *(uint32_t*)&h1;
+            }
+            tmem_st32(tmem_s(b) + lane_addr, packed);
+            const float sum = (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+            l = l * corr + sum;
+            // O of the blocks so far must be complete before it is rescaled, and before P V of this block is issued
             if (b > 0) {
-                if (!mb::wait(o_full, ph_blk ^ 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
+                if (!mb::wait(o_full, (b - 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
@@ -319,42 +407,25 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                         for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(__uint_as_float(raw[j]) * corr);
                         tmem_st32(tmem_o + lane_addr + c * 32, raw);
                     }
-                    tmem_st_wait();
                 }
             }
-            const float use = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum = 0.0f;
-            // P as bfloat16 over the K tile, swizzled K-major: row r, chunk c (8 keys) at chunk c ^ (r & 7)
-            unsigned char* prow = k_tile + r * 128;
-#pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                float e[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { e[j] = exp2f(s[c * 8 + j] - use); sum += e[j]; }
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(e[4], e[5]), h3 = __floats2bfloat162_rn(e[6], e[7]);
-                uint4 v;
-                v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
-                *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = v;
-            }
-            l = l * corr + sum;
             if (b == n_blocks - 1) {
-                // value rows after the tile's last token inside its page may hold anything: zero them (V has landed:
-                // the S product of this block waited for the same copy)
-                unsigned char* v_tile = k_tile + KV_BYTES;
+                // value rows after the tile's last token inside its page may hold anything: zero them
+                if (!mb::wait(&v_full[stage], use_parity(b), p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
+                unsigned char* v_tile = v_ring + stage * KV_BYTES;
                 const int first_bad = z_last - key0 + 1;
                 for (int idx = r; idx < (BN - first_bad) * 16; idx += 128) {
                     const int row = first_bad + idx / 16, c = idx % 16;
                     *(uint4*)(v_tile + (c >> 3) * HALF_KV + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the zeros, before the tensor core reads them
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P (and the zeros) before the tensor core reads them
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mb::arrive(p_full);
-            ph_blk ^= 1;
         }
-        if (ok) ok = mb::wait(o_full, ph_blk ^ 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX);
+        if (ok && n_blocks > 0) ok = mb::wait(o_full, (n_blocks - 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX);
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -438,7 +509,7 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
                                        const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
                                        int window, float scale, int* error_flag, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out ||
-        !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0)
+        !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || !(scale > 0.0f))
         return fail(PH_ERR_ARG, "attention_prefill_tc5: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
     if (head_dim != D) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: head_dim %d is not %d", head_dim, D);
     if (page_size != 8 && page_size != 16)
