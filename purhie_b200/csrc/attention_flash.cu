@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
     const uint32_t q_tile = smem_u32(smem);
     const uint32_t kv_tiles = q_tile + BM * D * 2;            // [2 buffers][K, V]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    const int tile = blockIdx.y, h = blockIdx.x;                   // heads of one tile start together; the caller lists long tiles first
     const int seg = tile_seg[tile], first = tile_first[tile];      // first: index of the tile's first token in its portion
     const int row0 = seg_start[seg], q_len = seg_start[seg + 1] - row0;
     const int ctx_len = seg_ctx_len[seg];
@@ -274,10 +274,10 @@ PH_EXPORT int ph_attention_prefill(const void* q, const void* k_base, const void
         n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || window < 0)
         return fail(PH_ERR_ARG, "attention_prefill: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
     if (D != 64 && D != 128) return fail(PH_ERR_UNSUPPORTED, "attention_prefill: head_dim %d is not 64 or 128", D);
-    if (HQ > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill: %d heads exceed the grid", HQ);
+    if (n_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill: %d tiles exceed the grid", n_tiles);
     if (n_tiles == 0) return PH_OK;
     const float scale_log2 = scale * LOG2E;
-    dim3 grid(n_tiles, HQ);
+    dim3 grid(HQ, n_tiles);
 #define LAUNCH(DD)                                                                                               \
     do {                                                                                                         \
         const int bytes = 64 * DD * 2 + 4 * BLOCK_KEYS * DD * 2;                                                 \

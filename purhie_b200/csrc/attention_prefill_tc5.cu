@@ -200,8 +200,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint32_t* tmem_slot = (uint32_t*)(o_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // long tiles first: the grid's first blocks are the tiles with the most keys
-    const int tile = p.n_tiles - 1 - (int)blockIdx.x, h = blockIdx.y;
+    // the heads of one tile start together; the caller lists the tiles with the most keys first
+    const int tile = blockIdx.y, h = blockIdx.x;
     const int seg = p.tile_seg[tile], first = p.tile_first[tile];
     const int row0 = p.seg_start[seg], q_len = p.seg_start[seg + 1] - row0;
     const int ctx_len = p.seg_ctx_len[seg];
@@ -516,7 +516,7 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
         return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: pages of %d tokens (8 or 16 are taken)", page_size);
     if (page_stride % D || (((uintptr_t)q | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)out) & 15))
         return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: tensors must be 16-byte aligned, pages whole rows");
-    if (HQ > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: %d heads exceed the grid", HQ);
+    if (n_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: %d tiles exceed the grid", n_tiles);
     if (n_tiles == 0) return PH_OK;
     const long long rows_per_page = page_stride / D;
     const long long rows = (long long)(num_pages - 1) * rows_per_page + (long long)HKV * page_size;
@@ -544,6 +544,6 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
             return fail(PH_ERR_LAUNCH, "attention_prefill_tc5: cannot reserve %d bytes of shared memory", SMEM_BYTES);
         configured = true;
     }
-    launch_overlapped(attention_prefill_tc5_kernel, dim3(n_tiles, HQ), dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
+    launch_overlapped(attention_prefill_tc5_kernel, dim3(HQ, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
     return check_launch("attention_prefill_tc5");
 }

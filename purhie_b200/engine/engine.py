@@ -213,6 +213,11 @@ class Engine:
                 for first in range(0, n, Q_TILE_LARGE):
                     big_seg.append(s)
                     big_first.append(first)
+        # the tiles that look furthest back come first: the attention grid starts them first, and the short ones
+        # fill the tail
+        for segs, firsts, rows in ((tile_seg, tile_first, Q_TILE), (big_seg, big_first, Q_TILE_LARGE)):
+            order = sorted(range(len(segs)), key=lambda i: -(ctx_lens[segs[i]] - q_lens[segs[i]] + min(firsts[i] + rows, q_lens[segs[i]])))
+            segs[:], firsts[:] = [segs[i] for i in order], [firsts[i] for i in order]
         widths = []
         for g in cache.groups:
             w = max(len(cache.block_table(e.request_id, g.index)) for e in entries)
