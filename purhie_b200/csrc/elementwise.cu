@@ -57,8 +57,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
 
 // The same with four consecutive elements per thread and all loads of a row in flight at once: a decode step
 // has a handful of rows, so the time of this kernel is the latency of its loads, not their volume.  E % 4 == 0,
-// every pointer 16-byte aligned (8 for bfloat16); the block has ceil(E / 4) threads rounded up to a warp, at
-// most 1024, so the order of the additions still depends on E only.
+// every pointer 16-byte aligned (8 for bfloat16).  The block has ceil(E / 4) threads rounded up to a warp, at
+// most 1024; with a thousand rows or more it has 256, so that an SM holds rows in different phases.  The order
+// of the additions depends on E only, not on the block's width.
 template <typename T> struct Vec4 { };
 template <> struct Vec4<float> {
     static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -82,17 +83,18 @@ template <typename TA, typename TY, int MAX_IT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
                                        const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
-    __shared__ float scratch[32];
+    __shared__ float scratch[128];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * E;
     float4 v[MAX_IT];
-    float ss = 0.0f;
+    float ss[MAX_IT];
 #pragma unroll
     for (int it = 0; it < MAX_IT; ++it) {
         const int i = (it * blockDim.x + threadIdx.x) * 4;
+        ss[it] = 0.0f;
         if (i < E) {
             float4 acc = Vec4<float>::load(xr + i);
             if (add) {
@@ -110,17 +112,22 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                 if (write_x) Vec4<float>::store(xr + i, acc);
             }
             v[it] = acc;
-            ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+            ss[it] = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
         }
     }
     if (!weight) return;
-    // block sum in a fixed order: lanes, then warps
-    ss = warp_sum(ss);
+    // The sum in an order that the block's width does not change: each run of 32 consecutive vectors by a
+    // butterfly, the runs' sums in groups of 32 by another, the groups in turn.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    if (lane == 0) scratch[warp] = ss;
+#pragma unroll
+    for (int it = 0; it < MAX_IT; ++it) {
+        const float part = warp_sum(ss[it]);
+        if (lane == 0) scratch[it * nwarps + warp] = part;
+    }
     __syncthreads();
-    float tot = lane < nwarps ? scratch[lane] : 0.0f;
-    tot = warp_sum(tot);
+    const int n_parts = (E / 4 + 31) / 32;
+    float tot = 0.0f;
+    for (int g = 0; g < n_parts; g += 32) tot += warp_sum(g + lane < n_parts ? scratch[g + lane] : 0.0f);
     const float inv = rsqrtf(tot / (float)E + eps);
     TY* yr = y + (size_t)r * E;
 #pragma unroll
@@ -208,8 +215,11 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
     const bool aligned = E % 4 == 0 && E <= 16384 && ((uintptr_t)x & 15) == 0 && (!weight || ((uintptr_t)weight & 15) == 0) &&
                          (!y || ((uintptr_t)y & 15) == 0) && (!add || (((uintptr_t)add & 15) == 0 && add_split_stride % 4 == 0));
     if (aligned) {
+        // few rows: as many threads per row as it has vectors (latency); many rows: blocks of 256, so that several
+        // rows per SM are in different phases (load, reduce, store) at once
         int threads = ((E / 4 + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
+        if (n_out >= 1024 && E <= 4096 && threads > 256) threads = 256;
         const int iters = (E / 4 + threads - 1) / threads;
 #define LAUNCH_VEC(TA, TY, IT)                                                                                          \
         launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT>, dim3(n_out), dim3(threads), 0, stream, x, (const TA*)add,   \

@@ -112,9 +112,10 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
     }
 }
 
-// Fast path for head_dim 128 rotated over its whole width in half pairs: one warp per (token, head), four
-// consecutive dimensions per lane, every load of the row in flight at once, the rotation partner (64 dimensions
-// away) fetched from lane ^ 16 by shuffle.  The order of the additions is the same for every launch shape.
+// Fast path for head_dim 128 rotated over its whole width in half pairs: one warp per token and HPW consecutive
+// heads (1 for a few tokens, where the launch is short of warps; 4 for many, where it is short of loads in flight),
+// four consecutive dimensions per lane, every load in flight at once, the rotation partner (64 dimensions away)
+// fetched from lane ^ 16 by shuffle.  The order of the additions is the same for every launch shape.
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
     const uint2 u = *reinterpret_cast<const uint2*>(p);
@@ -129,7 +130,7 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = u;
 }
 
-template <typename TI, typename TQ, typename TKV>
+template <typename TI, typename TQ, typename TKV, int HPW>
 __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits, long long split_stride,
                                          const float* __restrict__ bias, const float* __restrict__ q_w,
                                          const float* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
@@ -141,63 +142,76 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y * WARPS + warp;
+    const int head0 = (blockIdx.y * WARPS + warp) * HPW;      // this warp's HPW consecutive heads of token t
     const int t = blockIdx.x;
     const int n_heads = HQ + 2 * HKV;
-    if (head >= n_heads) return;
+    if (head0 >= n_heads) return;
     const int d0 = lane * 4;
-    const TI* src = qkv + (size_t)t * n_heads * D + (size_t)head * D + d0;
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int s0 = 0; s0 < splits; s0 += 4) {
-        float4 u[4];
+    // every head's loads are issued before any of them is used
+    float4 v[HPW];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            u[j] = s0 + j < splits ? ld4(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int i = 0; i < HPW; ++i) {
+        v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (head0 + i >= n_heads) continue;
+        const TI* src = qkv + (size_t)t * n_heads * D + (size_t)(head0 + i) * D + d0;
+        for (int s0 = 0; s0 < splits; s0 += 4) {
+            float4 u[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (s0 + j < splits) { v.x += u[j].x; v.y += u[j].y; v.z += u[j].z; v.w += u[j].w; }
+            for (int j = 0; j < 4; ++j)
+                u[j] = s0 + j < splits ? ld4(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (s0 + j < splits) { v[i].x += u[j].x; v[i].y += u[j].y; v[i].z += u[j].z; v[i].w += u[j].w; }
+        }
     }
-    if (bias) {
-        const float4 b = ld4(bias + (size_t)head * D + d0);
-        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-    }
-    const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
-    if (!is_q && !is_k) {
-        if (!slot_mapping) return;
-        const int slot = slot_mapping[t];
-        if (slot < 0) return;
-        const int h = head - HQ - HKV;
-        st4(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, v);
-        return;
-    }
-    const float* w = is_q ? q_w : k_w;
-    if (w) {
-        const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-        const float inv = rsqrtf(ss / (float)D + eps);
-        const float4 g = ld4(w + d0);
-        v.x = v.x * inv * g.x; v.y = v.y * inv * g.y; v.z = v.z * inv * g.z; v.w = v.w * inv * g.w;
-    }
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), sn = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (cos_sin) {
         int pos = positions[t];
         pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
         const int j = (lane & 15) * 4;                       // pair index of this lane's first dimension
-        const float4 c = ld4(cos_sin + (size_t)pos * D + j), sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
-        float4 o;
-        o.x = __shfl_xor_sync(0xffffffffu, v.x, 16); o.y = __shfl_xor_sync(0xffffffffu, v.y, 16);
-        o.z = __shfl_xor_sync(0xffffffffu, v.z, 16); o.w = __shfl_xor_sync(0xffffffffu, v.w, 16);
-        if (lane < 16) {       // first half: a cos - b sin
-            v.x = v.x * c.x - o.x * sn.x; v.y = v.y * c.y - o.y * sn.y; v.z = v.z * c.z - o.z * sn.z; v.w = v.w * c.w - o.w * sn.w;
-        } else {               // second half: a sin + b cos (a is the partner)
-            v.x = o.x * sn.x + v.x * c.x; v.y = o.y * sn.y + v.y * c.y; v.z = o.z * sn.z + v.z * c.z; v.w = o.w * sn.w + v.w * c.w;
-        }
+        c = ld4(cos_sin + (size_t)pos * D + j);
+        sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
     }
-    if (is_q) {
-        st4(q_out + ((size_t)t * HQ + head) * D + d0, v);
-    } else if (slot_mapping) {
-        const int slot = slot_mapping[t];
-        if (slot < 0) return;
-        const int h = head - HQ;
-        st4(k_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, v);
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int head = head0 + i;
+        if (head >= n_heads) break;
+        float4 x = v[i];
+        if (bias) {
+            const float4 b = ld4(bias + (size_t)head * D + d0);
+            x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+        }
+        const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
+        if (!is_q && !is_k) {
+            if (slot < 0) continue;
+            const int h = head - HQ - HKV;
+            st4(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, x);
+            continue;
+        }
+        const float* w = is_q ? q_w : k_w;
+        if (w) {
+            const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+            const float inv = rsqrtf(ss / (float)D + eps);
+            const float4 g = ld4(w + d0);
+            x.x = x.x * inv * g.x; x.y = x.y * inv * g.y; x.z = x.z * inv * g.z; x.w = x.w * inv * g.w;
+        }
+        if (cos_sin) {
+            float4 o;
+            o.x = __shfl_xor_sync(0xffffffffu, x.x, 16); o.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+            o.z = __shfl_xor_sync(0xffffffffu, x.z, 16); o.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+            if (lane < 16) {       // first half: a cos - b sin
+                x.x = x.x * c.x - o.x * sn.x; x.y = x.y * c.y - o.y * sn.y; x.z = x.z * c.z - o.z * sn.z; x.w = x.w * c.w - o.w * sn.w;
+            } else {               // second half: a sin + b cos (a is the partner)
+                x.x = o.x * sn.x + x.x * c.x; x.y = o.y * sn.y + x.y * c.y; x.z = o.z * sn.z + x.z * c.z; x.w = o.w * sn.w + x.w * c.w;
+            }
+        }
+        if (is_q) {
+            st4(q_out + ((size_t)t * HQ + head) * D + d0, x);
+        } else if (slot >= 0) {
+            const int h = head - HQ;
+            st4(k_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, x);
+        }
     }
 }
 
@@ -223,10 +237,21 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
                       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)bias |
                         (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
     if (fast) {
+        const int n_heads = HQ + 2 * HKV;
+        const bool many = (long long)T * n_heads >= 16384;      // enough warps to fill the device four heads each
+        const int hpw = many ? 4 : 1;
+        const dim3 fgrid(T, (n_heads + WARPS * hpw - 1) / (WARPS * hpw));
 #define LAUNCH_FAST(TI, TQ, TKV)                                                                                    \
-    launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV>, grid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, splits,   \
-                      split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions, slot_mapping, (TQ*)q_out, \
-                      (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV)
+    do {                                                                                                            \
+        if (many)                                                                                                   \
+            launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV, 4>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
+                              splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV); \
+        else                                                                                                        \
+            launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV, 1>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
+                              splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV); \
+    } while (0)
         PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_FAST(TI, TQ, TKV))));
 #undef LAUNCH_FAST
         return check_launch("qk_norm_rope");
