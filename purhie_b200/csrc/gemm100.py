@@ -3,7 +3,7 @@
 Few tokens (decoding, short portions): the weight fills the 128-row side of the tensor-core instruction
 and the tokens the other side ("swapped"), K is split over CTAs so that all SMs stream weights, and the
 float32 partial results are summed by the kernel that consumes the product.  Many tokens: 128-token by
-256-feature tiles.
+256-feature tiles, and 256 by 256 on pairs of CTAs (cta_group::2) once those fill the device.
 """
 from __future__ import annotations
 
@@ -18,6 +18,8 @@ from .ops import KernelError, call, register_signatures
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_void_p],
+    "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                  c_void_p],
 })
 
 BLOCK_K = 64
@@ -74,6 +76,20 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
     return out
 
 
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, max_clusters: int = 0, swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T on pairs of CTAs (cta_group::2), tiles of 256 x 256; ``swiglu`` as in gemm."""
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise KernelError(f"gemm_tcgen05_pair: {name} must be a contiguous bfloat16 CUDA tensor")
+    N, K = w.shape
+    M = x.numel() // K
+    if x.shape[-1] != K or out.numel() != M * (N // 2 if swiglu else N) or not out.is_contiguous():
+        raise KernelError(f"gemm_tcgen05_pair: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    call("gemm100", "ph_gemm_bf16_tcgen05_pair", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
+         max_clusters, 1 if swiglu else 0, error_flag(x.device).data_ptr(), ops._stream())
+    return out
+
+
 def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     """(swapped, block_n, splits) for a product of M tokens with an [N, K] weight.
 
@@ -99,17 +115,30 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     return True, block_n, splits
 
 
+def pair_pays(M: int, N: int, sms: int) -> bool:
+    """Whether the product runs on pairs of CTAs: when its tiles of 256 x 256 fill at least one round of the pairs.
+    Below that the one-CTA kernel, whose tiles are half as tall, keeps more SMs busy."""
+    return M > 128 and N > 128 and (-(-M // 256)) * (-(-N // 256)) >= sms // 2
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool,
            fuse_swiglu: bool = False):
     """The product through the tcgen05 kernel.  ``fuse_swiglu`` (w holds (gate, up) row pairs): when the plain
     orientation runs, the activation is applied in the epilogue and the result [M, N / 2] is marked activated."""
     from ..parts.base import Addend
     N, K = w.shape
-    swapped, block_n, splits = plan(M, N, K, sm_count(x.device), allow_split)
+    sms = sm_count(x.device)
+    swapped, block_n, splits = plan(M, N, K, sms, allow_split)
+    pair = not swapped and splits == 1 and pair_pays(M, N, sms)
     if fuse_swiglu and not swapped and splits == 1 and N % 2 == 0:
         out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
-        gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
+        if pair:
+            gemm_pair(x[:M], w, out, swiglu=True)
+        else:
+            gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
         return Addend(out, 1, activated=True)
+    if pair:
+        return Addend(gemm_pair(x[:M], w, ctx.workspace.get(out_name, (M, N), out_dtype)), 1)
     if splits > 1:
         out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)
     else:

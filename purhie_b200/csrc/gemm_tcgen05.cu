@@ -173,6 +173,91 @@ template <int BN> struct TileConfig {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
+// One chunk of CH accumulator columns of row a, starting at column b0 + c of the tile, to its place in out.
+template <int CH>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t* r, int a, int b0, int c, size_t split_off) {
+    if (a >= p.rows_a) return;
+    if (p.swiglu) {
+        // the activation in the epilogue: the product itself never goes to memory
+        const size_t base = (size_t)a * p.ld + (size_t)((b0 + c) >> 1);
+        float h[CH / 2];
+#pragma unroll
+        for (int j = 0; j < CH / 2; ++j) {
+            const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+            h[j] = g / (1.0f + __expf(-g)) * u;
+        }
+        const bool full_chunk = (b0 + c + CH <= p.rows_b);
+        if (p.out_bf16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
+            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CH / 2; j += 8) {
+                    uint4 v;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(h[j], h[j + 1]), h1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), h3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
+                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
+                    *(uint4*)(o + j) = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CH / 2; ++j)
+                    if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = __float2bfloat16_rn(h[j]);
+            }
+        } else {
+            float* o = (float*)p.out + base;
+#pragma unroll
+            for (int j = 0; j < CH / 2; ++j)
+                if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = h[j];
+        }
+    } else if (!p.swapped) {
+        const size_t base = split_off + (size_t)a * p.ld + (size_t)(b0 + c);
+        const bool full_chunk = (b0 + c + CH <= p.rows_b);
+        if (p.out_bf16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
+            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CH; j += 8) {
+                    uint4 v;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
+                    *(uint4*)(o + j) = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                    if (b0 + c + j < p.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+        } else {
+            float* o = (float*)p.out + base;
+            if (full_chunk && ((uintptr_t)o & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CH; j += 4)
+                    *(uint4*)(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                    if (b0 + c + j < p.rows_b) o[j] = __uint_as_float(r[j]);
+            }
+        }
+    } else {
+        // transposed: this thread's accumulator row is output feature a; lanes are neighbours in a
+        if (p.out_bf16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + split_off + a;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        } else {
+            float* o = (float*)p.out + split_off + a;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __uint_as_float(r[j]);
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, TileConfig<BN>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -314,87 +399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint32_t r[CH];
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
-                if (a < p.rows_a) {
-                    if (p.swiglu) {
-                        // the activation in the epilogue: the product itself never goes to memory
-                        const size_t base = (size_t)a * p.ld + (size_t)((b0 + c) >> 1);
-                        float h[CH / 2];
-#pragma unroll
-                        for (int j = 0; j < CH / 2; ++j) {
-                            const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-                            h[j] = g / (1.0f + __expf(-g)) * u;
-                        }
-                        const bool full_chunk = (b0 + c + CH <= p.rows_b);
-                        if (p.out_bf16) {
-                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
-                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
-#pragma unroll
-                                for (int j = 0; j < CH / 2; j += 8) {
-                                    uint4 v;
-                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(h[j], h[j + 1]), h1 = __floats2bfloat162_rn(h[j + 2], h[j + 3]);
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(h[j + 4], h[j + 5]), h3 = __floats2bfloat162_rn(h[j + 6], h[j + 7]);
-                                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
-                                    *(uint4*)(o + j) = v;
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < CH / 2; ++j)
-                                    if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = __float2bfloat16_rn(h[j]);
-                            }
-                        } else {
-                            float* o = (float*)p.out + base;
-#pragma unroll
-                            for (int j = 0; j < CH / 2; ++j)
-                                if (b0 + c + 2 * j + 1 < p.rows_b) o[j] = h[j];
-                        }
-                    } else if (!p.swapped) {
-                        const size_t base = split_off + (size_t)a * p.ld + (size_t)(b0 + c);
-                        const bool full_chunk = (b0 + c + CH <= p.rows_b);
-                        if (p.out_bf16) {
-                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + base;
-                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
-#pragma unroll
-                                for (int j = 0; j < CH; j += 8) {
-                                    uint4 v;
-                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                                    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1; v.z = *(uint32_t*)&h2; v.w = *(uint32_t*)&h3;
-                                    *(uint4*)(o + j) = v;
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < CH; ++j)
-                                    if (b0 + c + j < p.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                            }
-                        } else {
-                            float* o = (float*)p.out + base;
-                            if (full_chunk && ((uintptr_t)o & 15) == 0) {
-#pragma unroll
-                                for (int j = 0; j < CH; j += 4)
-                                    *(uint4*)(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < CH; ++j)
-                                    if (b0 + c + j < p.rows_b) o[j] = __uint_as_float(r[j]);
-                            }
-                        }
-                    } else {
-                        // transposed: this thread's accumulator row is output feature a; lanes are neighbours in a
-                        if (p.out_bf16) {
-                            __nv_bfloat16* o = (__nv_bfloat16*)p.out + split_off + a;
-#pragma unroll
-                            for (int j = 0; j < CH; ++j)
-                                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                        } else {
-                            float* o = (float*)p.out + split_off + a;
-#pragma unroll
-                            for (int j = 0; j < CH; ++j)
-                                if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __uint_as_float(r[j]);
-                        }
-                    }
-                }
+                store_chunk<CH>(p, r, a, b0, c, split_off);
             }
             tc_fence_before();
             __syncwarp();
@@ -407,6 +412,189 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---- two CTAs on one tile (cta_group::2) ---------------------------------------------------------------
+//
+// Plain orientation, many tokens: a cluster of two CTAs (on the two SMs of a pair) computes one tile of 256
+// tokens x 256 features.  Each CTA loads its own 128 rows of A and its own 128 rows of B per block of K (half the
+// shared-memory traffic per flop of the one-CTA tile, and six stages instead of four in the same space); the
+// leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256, N = 256, which reads A from each
+// CTA's own shared memory, B from both, and leaves each CTA's 128 rows x 256 columns of the result in its own
+// tensor memory.  Who signals whom:
+//   full[s]      in the leader: the copies of both CTAs complete there (TMA .cta_group::2 may complete on the
+//                peer's barrier), the leader's producer announces the bytes of both; the leader's MMA thread waits;
+//   empty[s]     in each CTA: the leader's tcgen05.commit reaches both (commit's own cluster multicast; no load is
+//                multicast);
+//   acc_full[a]  in each CTA, by the same kind of commit; acc_empty[a] in the leader, counted in by the eight
+//                epilogue warps of both CTAs.
+// The cluster is synchronised once after the barriers are initialised and once before tensor memory is freed, so
+// that no CTA's shared memory goes away while its peer may still signal it.
+constexpr int PAIR_BN = 256;                      // features of the pair's tile
+constexpr int PAIR_HALF = PAIR_BN / 2;            // rows of B each CTA loads
+constexpr int PAIR_B_BYTES = PAIR_HALF * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_TMEM_COLS = 2 * PAIR_BN;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of the same location in the CTA of the given rank.
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c_inner, int c_row) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c_inner), "r"(c_row) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, when the MMAs issued so far are complete, on the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    constexpr int STAGES = PAIR_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(smem + STAGES * PAIR_STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PAIR_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int a_tiles = (p.rows_a + 2 * BM - 1) / (2 * BM), b_tiles = (p.rows_b + PAIR_BN - 1) / PAIR_BN;
+    const int work_total = a_tiles * b_tiles;
+    const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;
+
+    pdl_launch_dependents();
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int w = first; w < work_total && ok; w += stride) {
+                const int a0 = (w % a_tiles) * 2 * BM + (int)rank * BM, b0 = (w / a_tiles) * PAIR_BN + (int)rank * PAIR_HALF;
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) { ok = false; break; }
+                    const uint32_t bar = cluster_addr(&full[stage], 0);
+                    // The leader announces the bytes of both CTAs on its own barrier (a local arrive: one at cluster
+                    // scope costs most of a microsecond).  The peer's bytes may land before that: the count of bytes
+                    // owed may run negative inside a phase, and the phase still needs the leader's arrival.
+                    if (leader) mbar_arrive_expect_tx(&full[stage], 2 * PAIR_STAGE_BYTES);
+                    tma_load_2d_pair(smem_a + stage * A_BYTES, &map_a, bar, kb * BK, a0);
+                    tma_load_2d_pair(smem_b + stage * PAIR_B_BYTES, &map_b, bar, kb * BK, b0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // Do not leave while copies may still be in flight: wait until the MMAs released every stage.
+            for (int s = 0; s < STAGES && ok; ++s) {
+                if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) break;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_idesc(2 * BM, PAIR_BN);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int w = first; w < work_total && ok; w += stride) {
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + (uint32_t)(acc * PAIR_BN);
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * A_BYTES));
+                    const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * PAIR_B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(d_addr, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[stage]);       // frees the stage in both CTAs
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&acc_full[acc]);          // the accumulator halves are complete in both CTAs
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        pdl_wait();
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int w = first; w < work_total && ok; w += stride) {
+            const int a0 = (w % a_tiles) * 2 * BM + (int)rank * BM, b0 = (w / a_tiles) * PAIR_BN;
+            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
+            tc_fence_after();
+            const int a = a0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PAIR_BN);
+#pragma unroll 1
+            for (int c = 0; c < PAIR_BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                store_chunk<32>(p, r, a, b0, c, 0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // nothing of the peer may still reach this CTA
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(PAIR_TMEM_COLS) : "memory");
     }
 }
 
@@ -483,9 +671,56 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     return check_launch("gemm_tcgen05");
 }
 
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_clusters, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess)
+            return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cannot reserve %d bytes of shared memory", PAIR_SMEM_BYTES);
+        configured = true;
+    }
+    const int work = ((p.rows_a + 2 * BM - 1) / (2 * BM)) * ((p.rows_b + PAIR_BN - 1) / PAIR_BN);
+    int clusters = sm_count() / 2;
+    if (max_clusters > 0 && max_clusters < clusters) clusters = max_clusters;
+    if (work < clusters) clusters = work;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, ma, mb, p) != cudaSuccess) {}
+    return check_launch("gemm_tcgen05_pair");
+}
+
 }  // namespace
 
 PH_DEFINE_LAST_ERROR(ph_gemm100)
+
+// The same product on pairs of CTAs (tcgen05 cta_group::2): tiles of 256 tokens x 256 features, plain orientation,
+// one split.  max_clusters: 0 or a cap on the number of CTA pairs.
+PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
+                                        int max_clusters, int swiglu, int* error_flag, cudaStream_t stream) {
+    if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "gemm_tcgen05_pair: bad arguments (M %d, N %d, K %d)", M, N, K);
+    if (K % 8) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05_pair: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05_pair: operands must be 16-byte aligned");
+    if (swiglu && (N & 1)) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue needs an even N");
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, x, M, K, BM) || !make_map(&mb, w, N, K, PAIR_HALF))
+        return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cuTensorMapEncodeTiled failed (rows %d / %d, K %d)", M, N, K);
+    GemmParams p;
+    p.rows_a = M; p.rows_b = N; p.K = K;
+    p.a_tiles = 0; p.b_tiles = 0; p.splits = 1; p.kblocks = (K + BK - 1) / BK;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.ld = swiglu ? N / 2 : N;
+    p.split_stride = (long long)M * N; p.error_flag = error_flag;
+    return launch_pair(ma, mb, p, max_clusters, stream);
+}
 
 // out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
 // side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).

@@ -101,6 +101,41 @@ def test_gemm_tcgen05_swiglu_epilogue(M, N, K, out_dtype):
     assert rel(out, g / (1 + torch.exp(-g)) * u) < (3e-5 if out_dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("M,N,K,max_clusters,swiglu", [
+    (256, 256, 64, 0, False),               # one tile, one block of K
+    (256, 256, 1024, 0, False),             # the stage ring wraps
+    (300, 520, 200, 0, False),              # ragged on every side, K not a multiple of 64; the second CTA's rows partly outside
+    (130, 136, 72, 0, False),               # the second CTA of the pair has two rows and eight features
+    (2048, 1024, 1024, 3, False),           # many tiles per pair: both accumulator buffers in use
+    (1024, 2048, 512, 0, True),
+    (2048, 6144, 256, 0, False),            # more tiles than pairs
+])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_pair(M, N, K, max_clusters, swiglu, out_dtype):
+    """Two CTAs on one 256 x 256 tile (cta_group::2): each loads its half of both operands, the leader issues."""
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=13), rnd(N, K, dtype=torch.bfloat16, seed=14, scale=0.2)
+    out = torch.full((M, N // 2) if swiglu else (M, N), float("nan"), dtype=out_dtype, device=DEV)
+    gemm100.gemm_pair(x, w, out, max_clusters=max_clusters, swiglu=swiglu)
+    gemm100.check_errors(DEV)
+    y = x.double() @ w.double().T
+    if swiglu:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g / (1 + torch.exp(-g)) * u
+    assert not torch.isnan(out).any()
+    assert rel(out, y) < (3e-5 if out_dtype == torch.float32 else 6e-3)
+
+
+def test_gemm_tcgen05_pair_equals_one_cta_kernel():
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(640, 448, dtype=torch.bfloat16, seed=15), rnd(1000, 448, dtype=torch.bfloat16, seed=16)
+    a, b = torch.empty(640, 1000, device=DEV), torch.empty(640, 1000, device=DEV)
+    gemm100.gemm(x, w, a, swapped=False, block_n=256)
+    gemm100.gemm_pair(x, w, b)
+    gemm100.check_errors(DEV)
+    assert torch.equal(a, b)                # the same products added in the same order of K
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     from purhie_b200.csrc import gemm100
     from purhie_b200.csrc.ops import KernelError
