@@ -356,8 +356,13 @@ class Model:
                 logits = eng.step(entries)
             except OutOfPages as e:
                 raise InferenceError(ERR_CONTEXT_FULL, str(e)) from e
+        # One copy of the step's logits (they live in scratch memory that the next step reuses); each sequence
+        # keeps a view of its row.  When every sampled row comes from this step, in order, the copy is sampled
+        # from as it is.
+        kept = logits.clone() if logits is not None else None
         row = 0
         rows, samplers, who = [], [], []
+        direct = True
         for i, st, toks, samples in owners:
             s = self._seqs[st.seq]
             s.tokens.extend(toks)
@@ -366,13 +371,15 @@ class Model:
                 results[i] = (True, None)
                 continue
             if toks:
-                s.logits = logits[row].clone()
+                s.logits = kept[row]
                 row += 1
+            else:
+                direct = False
             rows.append(s.logits)
             samplers.append(st.sampler)
             who.append((i, st))
         if rows:
-            toks_out = eng.sample(torch.stack(rows), samplers)
+            toks_out = eng.sample(kept if direct and len(rows) == kept.shape[0] else torch.stack(rows), samplers)
             for (i, st), tok in zip(who, toks_out):
                 results[i] = self._emit(st, int(tok))
         return results

@@ -246,12 +246,12 @@ class Engine:
         self._meta_turn ^= 1
         buf, event = self._meta_host[self._meta_turn]
         if buf is None or buf.numel() < total:
-            buf = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
+            buf = torch.empty(max(2 * total, 4096), dtype=torch.int32).pin_memory()
             event = torch.cuda.Event()
         else:
             event.synchronize()
         self._meta_host[self._meta_turn] = (buf, event)
-        buf[:total].copy_(torch.tensor(flat, dtype=torch.int32))
+        buf.numpy()[:total] = flat                     # straight into the pinned memory
         dev.copy_(buf[:total], non_blocking=True)
         event.record()
 
@@ -331,9 +331,9 @@ class Engine:
         # every row's logits are computed; the wanted ones are picked afterwards
         all_rows = torch.arange(S, dtype=torch.int32, device=self.device) if g.rows is None else g.rows
         g.rows = all_rows
-        ctx, want_rows = self._context(lay, g.meta, g.workspace)
-        ctx.decode_max_ctx = ctx_bucket          # the number of attention splits must not change between replays
         if g.graph is None:
+            ctx, want_rows = self._context(lay, g.meta, g.workspace)
+            ctx.decode_max_ctx = ctx_bucket      # the number of attention splits must not change between replays
             # the first time: run the launches directly (this is the step's result, and whatever a kernel
             # sets up on first use is set up), then capture the same launches for the next time
             g.logits = self.model.forward(ctx, self.views, all_rows, S)
