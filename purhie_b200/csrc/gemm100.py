@@ -18,8 +18,8 @@ from .ops import KernelError, call, register_signatures
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_void_p],
-    "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                  c_void_p],
+    "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p],
 })
 
 BLOCK_K = 64
@@ -76,17 +76,19 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
     return out
 
 
-def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, max_clusters: int = 0, swiglu: bool = False) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T on pairs of CTAs (cta_group::2), tiles of 256 x 256; ``swiglu`` as in gemm."""
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: int = 1, max_clusters: int = 0,
+              swiglu: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T on pairs of CTAs (cta_group::2), tiles of 256 x 256; float32 partial sums
+    [splits, M, N] when splits > 1; ``swiglu`` as in gemm."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"gemm_tcgen05_pair: {name} must be a contiguous bfloat16 CUDA tensor")
     N, K = w.shape
     M = x.numel() // K
-    if x.shape[-1] != K or out.numel() != M * (N // 2 if swiglu else N) or not out.is_contiguous():
+    if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05_pair: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05_pair", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         max_clusters, 1 if swiglu else 0, error_flag(x.device).data_ptr(), ops._stream())
+         splits, max_clusters, 1 if swiglu else 0, error_flag(x.device).data_ptr(), ops._stream())
     return out
 
 
@@ -115,10 +117,32 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     return True, block_n, splits
 
 
-def pair_pays(M: int, N: int, sms: int) -> bool:
-    """Whether the product runs on pairs of CTAs: when its tiles of 256 x 256 fill at least one round of the pairs.
-    Below that the one-CTA kernel, whose tiles are half as tall, keeps more SMs busy."""
-    return M > 128 and N > 128 and (-(-M // 256)) * (-(-N // 256)) >= sms // 2
+def plan_many(M: int, N: int, K: int, sms: int, allow_split: bool, fused_epilogue: bool = False):
+    """(pair, splits) for a product of M >= 128 tokens in the plain orientation: the one-CTA kernel (tiles of 128
+    tokens x 256 features) or the pair kernel (256 x 256 on two SMs), and into how many parts K is cut.
+
+    Estimated cost in units of one block of K on one SM's tile: rounds of the CTAs (or pairs) times the item's
+    blocks (the pair spends 0.87 of a block's time per block: half the shared-memory traffic per flop) plus six for
+    an item's start and epilogue, plus the float32 partial results' way to memory and back when K is split.  A
+    fused epilogue (the activation) needs the whole sum in one place: no split."""
+    kblocks = -(-K // BLOCK_K)
+    best, choice = None, (False, 1)
+    split_options = (1, 2, 3, 4, 6, 8) if allow_split and not fused_epilogue else (1,)
+    for pair in (False, True):
+        if pair and (M <= 128 or N <= 128):
+            continue
+        tiles = (-(-M // 256) if pair else -(-M // 128)) * -(-N // 256)
+        slots = sms // 2 if pair else sms
+        for s in split_options:
+            if s > 1 and kblocks // s < 8:
+                continue
+            rounds = -(-(tiles * s) // slots)
+            cost = rounds * ((0.87 if pair else 1.0) * kblocks / s + 6.0)
+            if s > 1:
+                cost += 2.0 * s * M * N * 4 / 4.0e12 / 0.33e-6
+            if best is None or cost < best - 1e-9:
+                best, choice = cost, (pair, s)
+    return choice
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool,
@@ -129,19 +153,27 @@ def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torc
     N, K = w.shape
     sms = sm_count(x.device)
     swapped, block_n, splits = plan(M, N, K, sms, allow_split)
-    pair = not swapped and splits == 1 and pair_pays(M, N, sms)
-    if fuse_swiglu and not swapped and splits == 1 and N % 2 == 0:
+    pair = False
+    if not swapped and block_n == 256:
+        fused = fuse_swiglu and N % 2 == 0
+        pair, splits = plan_many(M, N, K, sms, allow_split, fused_epilogue=fused)
+        if fused:
+            out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
+            if pair:
+                gemm_pair(x[:M], w, out, swiglu=True)
+            else:
+                gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
+            return Addend(out, 1, activated=True)
+    elif fuse_swiglu and not swapped and splits == 1 and N % 2 == 0:
         out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
-        if pair:
-            gemm_pair(x[:M], w, out, swiglu=True)
-        else:
-            gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
+        gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
         return Addend(out, 1, activated=True)
-    if pair:
-        return Addend(gemm_pair(x[:M], w, ctx.workspace.get(out_name, (M, N), out_dtype)), 1)
     if splits > 1:
         out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)
     else:
         out = ctx.workspace.get(out_name, (M, N), out_dtype)
-    gemm(x[:M], w, out, swapped=swapped, block_n=block_n, splits=splits)
+    if pair:
+        gemm_pair(x[:M], w, out, splits=splits)
+    else:
+        gemm(x[:M], w, out, swapped=swapped, block_n=block_n, splits=splits)
     return Addend(out, splits)

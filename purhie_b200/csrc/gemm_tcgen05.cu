@@ -508,8 +508,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t tmem_base = *tmem_slot;
 
     const int a_tiles = (p.rows_a + 2 * BM - 1) / (2 * BM), b_tiles = (p.rows_b + PAIR_BN - 1) / PAIR_BN;
-    const int work_total = a_tiles * b_tiles;
+    const int work_total = a_tiles * b_tiles * p.splits;          // item w: split w % splits of tile w / splits
     const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;
+    auto k_range = [&](int w, int& kb0, int& kb1) {
+        const int split = w % p.splits;
+        kb0 = (int)((long long)p.kblocks * split / p.splits);
+        kb1 = (int)((long long)p.kblocks * (split + 1) / p.splits);
+    };
 
     pdl_launch_dependents();
     if (warp == 0) {
@@ -519,8 +524,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             uint32_t phase = 0;
             bool ok = true;
             for (int w = first; w < work_total && ok; w += stride) {
-                const int a0 = (w % a_tiles) * 2 * BM + (int)rank * BM, b0 = (w / a_tiles) * PAIR_BN + (int)rank * PAIR_HALF;
-                for (int kb = 0; kb < p.kblocks; ++kb) {
+                const int tile = w / p.splits;
+                const int a0 = (tile % a_tiles) * 2 * BM + (int)rank * BM, b0 = (tile / a_tiles) * PAIR_BN + (int)rank * PAIR_HALF;
+                int kb0, kb1;
+                k_range(w, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_PRODUCER)) { ok = false; break; }
                     const uint32_t bar = cluster_addr(&full[stage], 0);
                     // The leader announces the bytes of both CTAs on its own barrier (a local arrive: one at cluster
@@ -548,14 +556,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_addr = tmem_base + (uint32_t)(acc * PAIR_BN);
-                for (int kb = 0; kb < p.kblocks; ++kb) {
+                int kb0, kb1;
+                k_range(w, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, p.error_flag, PH_ERR_WAIT_MMA)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * A_BYTES));
                     const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * PAIR_B_BYTES));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16_pair(d_addr, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(d_addr, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty[stage]);       // frees the stage in both CTAs
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -571,7 +581,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int w = first; w < work_total && ok; w += stride) {
-            const int a0 = (w % a_tiles) * 2 * BM + (int)rank * BM, b0 = (w / a_tiles) * PAIR_BN;
+            const int tile = w / p.splits;
+            const int a0 = (tile % a_tiles) * 2 * BM + (int)rank * BM, b0 = (tile / a_tiles) * PAIR_BN;
+            const size_t split_off = (size_t)(w % p.splits) * (size_t)p.split_stride;
             if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
             tc_fence_after();
             const int a = a0 + q * 32 + lane;
@@ -581,7 +593,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
-                store_chunk<32>(p, r, a, b0, c, 0);
+                store_chunk<32>(p, r, a, b0, c, split_off);
             }
             tc_fence_before();
             __syncwarp();
@@ -678,7 +690,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
             return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cannot reserve %d bytes of shared memory", PAIR_SMEM_BYTES);
         configured = true;
     }
-    const int work = ((p.rows_a + 2 * BM - 1) / (2 * BM)) * ((p.rows_b + PAIR_BN - 1) / PAIR_BN);
+    const int work = ((p.rows_a + 2 * BM - 1) / (2 * BM)) * ((p.rows_b + PAIR_BN - 1) / PAIR_BN) * p.splits;
     int clusters = sm_count() / 2;
     if (max_clusters > 0 && max_clusters < clusters) clusters = max_clusters;
     if (work < clusters) clusters = work;
@@ -702,21 +714,24 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
 
 PH_DEFINE_LAST_ERROR(ph_gemm100)
 
-// The same product on pairs of CTAs (tcgen05 cta_group::2): tiles of 256 tokens x 256 features, plain orientation,
-// one split.  max_clusters: 0 or a cap on the number of CTA pairs.
+// The same product on pairs of CTAs (tcgen05 cta_group::2): tiles of 256 tokens x 256 features, plain orientation;
+// float32 partial results [splits][M, N] with splits > 1.  max_clusters: 0 or a cap on the number of CTA pairs.
 PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                        int max_clusters, int swiglu, int* error_flag, cudaStream_t stream) {
+                                        int splits, int max_clusters, int swiglu, int* error_flag, cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05_pair: bad arguments (M %d, N %d, K %d)", M, N, K);
     if (K % 8) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05_pair: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05_pair: operands must be 16-byte aligned");
-    if (swiglu && (N & 1)) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue needs an even N");
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1 || splits > kblocks) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: %d splits for %d blocks of K", splits, kblocks);
+    if (splits > 1 && out_dtype != PH_F32) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: partial results are float32");
+    if (swiglu && ((N & 1) || splits > 1)) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue needs an even N and one split");
     CUtensorMap ma, mb;
     if (!make_map(&ma, x, M, K, BM) || !make_map(&mb, w, N, K, PAIR_HALF))
         return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cuTensorMapEncodeTiled failed (rows %d / %d, K %d)", M, N, K);
     GemmParams p;
     p.rows_a = M; p.rows_b = N; p.K = K;
-    p.a_tiles = 0; p.b_tiles = 0; p.splits = 1; p.kblocks = (K + BK - 1) / BK;
+    p.a_tiles = 0; p.b_tiles = 0; p.splits = splits; p.kblocks = kblocks;
     p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     return launch_pair(ma, mb, p, max_clusters, stream);

@@ -126,6 +126,26 @@ def test_gemm_tcgen05_pair(M, N, K, max_clusters, swiglu, out_dtype):
     assert rel(out, y) < (3e-5 if out_dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(512, 768, 2048, 2), (300, 520, 4104, 3), (1024, 1024, 8192, 8)])
+def test_gemm_tcgen05_pair_with_k_in_parts(M, N, K, splits):
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=17), rnd(N, K, dtype=torch.bfloat16, seed=18, scale=0.2)
+    out = torch.full((splits, M, N), float("nan"), device=DEV)
+    gemm100.gemm_pair(x, w, out, splits=splits)
+    gemm100.check_errors(DEV)
+    assert rel(out.double().sum(0), x.double() @ w.double().T) < 3e-5
+
+
+def test_plan_for_many_tokens_keeps_a_fused_epilogue_whole_and_fills_the_device():
+    from purhie_b200.csrc.gemm100 import plan_many
+    assert plan_many(2048, 24576, 4096, 148, True, fused_epilogue=True) == (True, 1)
+    assert plan_many(512, 24576, 4096, 148, True, fused_epilogue=True)[1] == 1
+    pair, splits = plan_many(512, 4096, 12288, 148, True)            # 32 tiles of 256 x 256 on 74 pairs: K is cut
+    assert splits > 1
+    assert plan_many(512, 4096, 12288, 148, False)[1] == 1
+    assert plan_many(128, 4096, 4096, 148, True)[0] is False         # one tile high: no second CTA to pair with
+
+
 def test_gemm_tcgen05_pair_equals_one_cta_kernel():
     from purhie_b200.csrc import gemm100
     x, w = rnd(640, 448, dtype=torch.bfloat16, seed=15), rnd(1000, 448, dtype=torch.bfloat16, seed=16)
