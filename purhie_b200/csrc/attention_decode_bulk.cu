@@ -127,7 +127,9 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
     }
     pdl_launch_dependents();
     __syncthreads();
-    pdl_wait();                       // the queries and this step's keys and values come from the kernel before
+    // The queries and this step's keys and values come from the kernel before this one: the consumers wait for
+    // it here, the producer only after it has requested what older steps wrote (below).
+    if (warp != CONSUMER_WARPS) pdl_wait();
 
     if (warp == CONSUMER_WARPS) {
         // ---- producer ----
@@ -139,6 +141,7 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
         int ok = 1;
         const int psh = p.page_shift, ppb = BLOCK_KEYS >> psh;              // pages per stage
         const int page_block = 2 * HALVES * p.page_size * 128;             // bytes of one page's box
+        bool waited = false;                                                // for the kernel in front
         for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
             const Item it = make_item(p, w);
             const int32_t* table = p.block_table + (size_t)p.row_seg[it.t] * p.table_stride;
@@ -153,6 +156,25 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
             __syncwarp();                                                    // the previous item's boxes are issued
             for (int j = lane; j < nb * ppb && j < PAGE_CACHE; j += 32) pages[j] = page_row(j);
             __syncwarp();
+            // The first item's leading blocks hold keys and values of earlier steps (block tables and positions were
+            // uploaded before the step began): they are requested while the kernel in front still runs.  The block
+            // with the token's own position, the last of the last split, is not among them.
+            int b_start = 0;
+            if (!waited) {
+                int n_pre = min(nb, STAGES);
+                if (it.split == p.splits - 1) n_pre = min(n_pre, nb - 1);
+                for (; b_start < n_pre; ++b_start) {
+                    if (lane == 0) mb::arrive_expect_tx(&full[stage], 2 * TILE);      // the ring is still empty
+                    __syncwarp();
+                    if (lane < ppb) {
+                        const int j = b_start * ppb + lane;
+                        tma_load_page(kv + stage * 2 * TILE + lane * page_block, &map_kv, &full[stage], j < PAGE_CACHE ? pages[j] : page_row(j));
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                pdl_wait();
+                waited = true;
+            }
             // the query rows of this kv head's group are contiguous: one copy
             if (lane == 0) {
                 ok = mb::wait(&q_empty[qi], q_phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER) ? 1 : 0;
@@ -164,7 +186,7 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             if (++qi == 2) { qi = 0; q_phase ^= 1; }
-            for (int b = 0; b < nb; ++b) {
+            for (int b = b_start; b < nb; ++b) {
                 if (lane == 0) {
                     ok = mb::wait(&empty[stage], phase ^ 1, p.error_flag, PH_ERR_WAIT_ATTN_PRODUCER) ? 1 : 0;
                     if (ok) mb::arrive_expect_tx(&full[stage], 2 * TILE);
@@ -179,6 +201,7 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (!waited) pdl_wait();                                            // a CTA without work
         if (lane == 0 && ok) {
             // do not leave while copies may be in flight: wait until the consumers released every stage
             for (int s = 0; s < STAGES; ++s) {
