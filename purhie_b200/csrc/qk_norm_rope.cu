@@ -112,8 +112,8 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
     }
 }
 
-// Fast path for head_dim 128 rotated over its whole width in half pairs: one warp per token and HPW consecutive
-// heads (1 for a few tokens, where the launch is short of warps; 4 for many, where it is short of loads in flight),
+// Fast path for head_dim 128 rotated over its whole width in half pairs, for a few tokens (where the launch is
+// short of warps): one warp per token and HPW consecutive heads (1 as launched),
 // four consecutive dimensions per lane, every load in flight at once, the rotation partner (64 dimensions away)
 // fetched from lane ^ 16 by shuffle.  The order of the additions is the same for every launch shape.
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -215,6 +215,129 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
     }
 }
 
+// The same for many tokens: eight consecutive dimensions per lane (one 16-byte load of bfloat16), a half-warp per
+// head, a warp walks ITERS pairs of heads of one token with every load issued first.  The sum of squares is added
+// in the order of the kernel above (four-element groups, then a butterfly over the 32 groups: here over 16 lanes
+// for the even and the odd group apart, then the two), so both give the same bits.  The rotation partner (64
+// dimensions away) sits eight lanes away in the same half-warp.
+struct F8 { float4 a, b; };
+__device__ __forceinline__ F8 ld8(const float* p) { return {ld4(p), ld4(p + 4)}; }
+__device__ __forceinline__ F8 ld8(const __nv_bfloat16* p) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    return {make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1])),
+            make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]))};
+}
+__device__ __forceinline__ void st8(float* p, const F8& v) { st4(p, v.a); st4(p + 4, v.b); }
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const F8& v) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v.a.x, v.a.y), h1 = __floats2bfloat162_rn(v.a.z, v.a.w);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v.b.x, v.b.y), h3 = __floats2bfloat162_rn(v.b.z, v.b.w);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void add4(float4& x, const float4& y) { x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+__device__ __forceinline__ float4 shfl4(const float4& v, int m) {
+    return make_float4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
+                       __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
+}
+// first half of the head: a cos - b sin; second half: a sin + b cos with a the partner
+__device__ __forceinline__ float4 rotate4(const float4& x, const float4& o, const float4& c, const float4& sn, bool first) {
+    if (first) return make_float4(x.x * c.x - o.x * sn.x, x.y * c.y - o.y * sn.y, x.z * c.z - o.z * sn.z, x.w * c.w - o.w * sn.w);
+    return make_float4(o.x * sn.x + x.x * c.x, o.y * sn.y + x.y * c.y, o.z * sn.z + x.z * c.z, o.w * sn.w + x.w * c.w);
+}
+
+template <typename TI, typename TQ, typename TKV, int ITERS>
+__global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int splits, long long split_stride,
+                                              const float* __restrict__ bias, const float* __restrict__ q_w,
+                                              const float* __restrict__ k_w, float eps, const float* __restrict__ cos_sin,
+                                              int max_pos, const int32_t* __restrict__ positions,
+                                              const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
+                                              TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
+                                              int page_size, int HQ, int HKV) {
+    constexpr int D = 128;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = lane >> 4, l16 = lane & 15;
+    const int head0 = (blockIdx.y * WARPS + warp) * 2 * ITERS + half;      // this half-warp's heads: head0, head0 + 2, ...
+    const int t = blockIdx.x;
+    const int n_heads = HQ + 2 * HKV;
+    const int d0 = l16 * 8;
+    F8 v[ITERS];
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+        v[i] = {make_float4(0.0f, 0.0f, 0.0f, 0.0f), make_float4(0.0f, 0.0f, 0.0f, 0.0f)};
+        const int head = head0 + 2 * i;
+        if (head >= n_heads) continue;
+        const TI* src = qkv + (size_t)t * n_heads * D + (size_t)head * D + d0;
+        for (int s0 = 0; s0 < splits; ++s0) {
+            const F8 u = ld8(src + (size_t)s0 * split_stride);
+            add4(v[i].a, u.a);
+            add4(v[i].b, u.b);
+        }
+    }
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float4 c0 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), c1 = c0, s0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), s1 = s0;
+    if (cos_sin) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+        const int j = (l16 & 7) * 8;                         // pair index of this lane's first dimension
+        const float* row = cos_sin + (size_t)pos * D;
+        c0 = ld4(row + j); c1 = ld4(row + j + 4);
+        s0 = ld4(row + 64 + j); s1 = ld4(row + 64 + j + 4);
+    }
+    const bool first = l16 < 8;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+        const int head = head0 + 2 * i;
+        const bool live = head < n_heads;                     // the shuffles below are run by every lane
+        F8 x = v[i];
+        if (bias && live) {
+            const F8 b = ld8(bias + (size_t)head * D + d0);
+            add4(x.a, b.a);
+            add4(x.b, b.b);
+        }
+        const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
+        const float* w = is_q ? q_w : k_w;
+        // sum of squares: the two four-element groups of the lane apart over the half-warp, then together
+        float p0 = x.a.x * x.a.x + x.a.y * x.a.y + x.a.z * x.a.z + x.a.w * x.a.w;
+        float p1 = x.b.x * x.b.x + x.b.y * x.b.y + x.b.z * x.b.z + x.b.w * x.b.w;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            p0 += __shfl_xor_sync(0xffffffffu, p0, o);
+            p1 += __shfl_xor_sync(0xffffffffu, p1, o);
+        }
+        F8 y = x;
+        if (w && (is_q || is_k) && live) {
+            const float inv = rsqrtf((p0 + p1) / (float)D + eps);
+            const F8 g = ld8(w + d0);
+            y.a = make_float4(x.a.x * inv * g.a.x, x.a.y * inv * g.a.y, x.a.z * inv * g.a.z, x.a.w * inv * g.a.w);
+            y.b = make_float4(x.b.x * inv * g.b.x, x.b.y * inv * g.b.y, x.b.z * inv * g.b.z, x.b.w * inv * g.b.w);
+        }
+        const float4 oa = shfl4(y.a, 8), ob = shfl4(y.b, 8);
+        if (!live) continue;
+        if (!is_q && !is_k) {
+            if (slot >= 0) {
+                const int h = head - HQ - HKV;
+                st8(v_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, x);
+            }
+            continue;
+        }
+        if (cos_sin) {
+            y.a = rotate4(y.a, oa, c0, s0, first);
+            y.b = rotate4(y.b, ob, c1, s1, first);
+        }
+        if (is_q) {
+            st8(q_out + ((size_t)t * HQ + head) * D + d0, y);
+        } else if (slot >= 0) {
+            const int h = head - HQ;
+            st8(k_base + (size_t)(slot / page_size) * page_stride + ((size_t)h * page_size + slot % page_size) * D + d0, y);
+        }
+    }
+}
+
 }  // namespace
 
 PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int splits, long long split_stride,
@@ -238,13 +361,13 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
                         (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0 && page_stride % 8 == 0;
     if (fast) {
         const int n_heads = HQ + 2 * HKV;
-        const bool many = (long long)T * n_heads >= 16384;      // enough warps to fill the device four heads each
-        const int hpw = many ? 4 : 1;
-        const dim3 fgrid(T, (n_heads + WARPS * hpw - 1) / (WARPS * hpw));
+        // enough tokens to fill the device with warps that walk three pairs of heads each: the wide kernel
+        const bool many = (long long)T * n_heads >= 16384 && page_stride % 8 == 0 && split_stride % 8 == 0;
+        const dim3 fgrid(T, many ? (n_heads + WARPS * 6 - 1) / (WARPS * 6) : (n_heads + WARPS - 1) / WARPS);
 #define LAUNCH_FAST(TI, TQ, TKV)                                                                                    \
     do {                                                                                                            \
         if (many)                                                                                                   \
-            launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV, 4>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
+            launch_overlapped(qk_norm_rope_d128_wide_kernel<TI, TQ, TKV, 3>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
                               splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
                               slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV); \
         else                                                                                                        \

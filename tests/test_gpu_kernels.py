@@ -487,3 +487,48 @@ def test_qk_norm_rope_kv_write(HQ, HKV, D, n_rot, interleaved, splits, dtype):
     # nothing but the mapped slots was touched
     untouched = pool.float().cpu().permute(0, 4, 1, 2, 3, 5).reshape(n_pages * ps, -1)[~written]
     assert torch.isnan(untouched).all()
+
+
+@pytest.mark.parametrize("HQ,HKV,splits,dtype,with_bias", [(32, 8, 1, torch.bfloat16, False), (5, 3, 2, torch.bfloat16, True),
+                                                          (32, 8, 1, torch.float32, False)])
+def test_qk_norm_rope_of_many_tokens_gives_the_bits_of_few(HQ, HKV, splits, dtype, with_bias):
+    """Many tokens run a kernel with eight dimensions per lane; a token's result must not depend on how many
+    tokens share its launch, so it is compared bit by bit with launches of a few tokens (the four-per-lane kernel)."""
+    from purhie_b200.csrc import ops
+    D, ps, eps = 128, 16, 1e-6
+    n_heads = HQ + 2 * HKV
+    T = -(-16384 // n_heads) + 37                 # enough for the wide kernel, and not a round number
+    n_pages, max_pos = -(-T // ps) + 1, T + 5
+    in_dtype = torch.float32 if splits > 1 else dtype
+    qkv = rnd(splits, T, n_heads * D, dtype=in_dtype, seed=21)
+    bias = rnd(n_heads * D, seed=22) * 0.1 if with_bias else None
+    qw, kw = rnd(D, seed=23) * 0.2 + 1.0, rnd(D, seed=24) * 0.2 + 1.0
+    g = torch.Generator().manual_seed(5)
+    pos = torch.randint(0, max_pos, (T,), generator=g).int().to(DEV)
+    slots = torch.randperm(n_pages * ps, generator=g)[:T].int().to(DEV)
+    slots[7] = -1
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e6 ** (-2.0 * torch.arange(D // 2, dtype=torch.float64) / D))[None, :]
+    table = torch.cat([ang.cos(), ang.sin()], 1).float().to(DEV)
+
+    def run(rows):
+        pool = torch.full((n_pages, 1, 2, HKV, ps, D), float("nan"), dtype=dtype, device=DEV)
+        q = torch.full((len(rows), HQ, D), float("nan"), dtype=dtype, device=DEV)
+        ops.qk_norm_rope_kv_write(qkv[:, rows].contiguous(), q, pos[rows].contiguous(), num_heads=HQ, num_kv_heads=HKV,
+                                  head_dim=D, eps=eps, q_norm=qw, k_norm=kw, bias=bias, cos_sin=table, n_rot=D,
+                                  slot_mapping=slots[rows].contiguous(), k_base=pool[0, 0, 0], v_base=pool[0, 0, 1],
+                                  page_stride=pool.stride(0), page_size=ps, splits=splits, interleaved=False)
+        return q, pool
+
+    q_all, pool_all = run(torch.arange(T, device=DEV))
+    assert not torch.isnan(q_all.float()).any()
+    few = torch.tensor([0, 7, 100, T - 1], device=DEV)
+    q_few, pool_few = run(few)
+    assert torch.equal(q_all[few], q_few)
+    for t in few.tolist():
+        sl = int(slots[t])
+        if sl >= 0:
+            assert torch.equal(pool_all[sl // ps, 0, :, :, sl % ps], pool_few[sl // ps, 0, :, :, sl % ps])
+    written = torch.zeros(n_pages * ps, dtype=torch.bool)
+    written[slots[slots >= 0].long().cpu()] = True
+    untouched = pool_all.float().cpu().permute(0, 4, 1, 2, 3, 5).reshape(n_pages * ps, -1)[~written]
+    assert torch.isnan(untouched).all()
