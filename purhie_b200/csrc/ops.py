@@ -63,6 +63,7 @@ _SIGNATURES = {
         "ph_gemm_simple": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ph_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
         "ph_sample_temperature": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
+        "ph_sample_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     },
 }
 _bound = {}
@@ -256,4 +257,20 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform:
         raise KernelError("sample_temperature: one temperature and one uniform number per row")
     call("core", "ph_sample_temperature", _ptr(logits), R, V, _ptr(temperature), _ptr(uniform), float(logit_range),
          _ptr(out), _stream())
+    return out
+
+
+CHAIN_MAX_K = 256          # most candidates the chain kernel keeps (KMAX in sampling.cu)
+CHAIN_ROW = [("uniform", "<f8"), ("top_p", "<f4"), ("log_min_p", "<f4"), ("temperature", "<f4"), ("top_k", "<i4")]
+
+
+def sample_chain(logits: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """top-k -> top-p -> min-p -> temperature -> draw for each row of ``logits``.  ``rows``: uint8 [R, 24] on the
+    device, one CHAIN_ROW record per row (top_k in 1 .. CHAIN_MAX_K, temperature > 0, log_min_p -inf for off)."""
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32); _need(rows, "rows", torch.uint8)
+    V = logits.shape[-1]
+    R = logits.numel() // V
+    if rows.numel() != 24 * R or out.numel() < R:
+        raise KernelError("sample_chain: one 24-byte record and one output per row")
+    call("core", "ph_sample_chain", _ptr(logits), R, V, _ptr(rows), _ptr(out), _stream())
     return out

@@ -5,6 +5,11 @@
 // exp((logit - max) / T), and the token is the first one, in id order, whose running sum exceeds
 // r * total, r being one uniform number in [0, 1) that the host draws per token.  Sums are in double.
 // Greedy: src/sampler.cpp:60-68.
+//
+// The chain with top-k on (src/sampler.cpp:72-92, 127-169): one CTA per row finds the k best tokens (by logit
+// descending, id ascending) with a radix selection over the order-preserving bits of the logits, sorts them, and
+// one thread then walks the reference's loops as they stand: top-p over the candidates, min-p, temperature and the
+// draw, in double where the reference uses double, with the uniform number the host drew for the token.
 #include "common.cuh"
 
 #include <math.h>
@@ -116,6 +121,155 @@ __global__ void __launch_bounds__(NT) sample_temperature_kernel(const float* __r
     }
 }
 
+constexpr int KMAX = 256;          // most candidates the chain kernel keeps
+
+// Bits that order like the floats they come from (-0 counted as +0).
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t b = __float_as_uint(f + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// One per-row parameter record, as the host packs it.
+struct ChainRow {
+    double uniform;
+    float top_p, log_min_p, temperature;     // log_min_p: -inf when min-p is off
+    int top_k;
+};
+
+__global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restrict__ logits, int V,
+                                                          const ChainRow* __restrict__ rows, int32_t* __restrict__ out) {
+    __shared__ int hist[256];
+    __shared__ uint32_t sel_prefix, sel_mask;
+    __shared__ int sel_remaining, n_gt;
+    __shared__ int scan[NT / 32];
+    __shared__ uint32_t cand_key[KMAX];
+    __shared__ int cand_id[KMAX], sorted_id[KMAX];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    const ChainRow prm = rows[blockIdx.x];
+    const int k = min(min(prm.top_k, V), KMAX);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) { sel_prefix = 0; sel_mask = 0; sel_remaining = k; n_gt = 0; }
+    // ---- the key of the k-th best: eight bits at a time, from the top ----
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += NT) hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = sel_prefix, mask = sel_mask;
+        for (int i0 = 0; i0 < V; i0 += NT) {
+            const int i = i0 + threadIdx.x;
+            const bool in = i < V;
+            const uint32_t key = in ? order_key(row[i]) : 0u;
+            const bool take = in && (key & mask) == prefix;
+            const int bin = take ? (int)((key >> shift) & 255u) : -1;
+            // lanes with the same bin add once
+            const unsigned peers = __match_any_sync(0xffffffffu, bin);
+            if (take && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int acc = 0, b = 255;
+            for (; b > 0; --b) {
+                if (acc + hist[b] >= sel_remaining) break;
+                acc += hist[b];
+            }
+            sel_remaining -= acc;                      // how many to take from bin b (and, in the end, of the key itself)
+            sel_prefix |= (uint32_t)b << shift;
+            sel_mask |= 255u << shift;
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = sel_prefix;
+    const int n_equal = sel_remaining;                 // tokens with exactly the k-th key to keep: the lowest ids
+    // ---- collect: everything above the k-th key, then the first n_equal with the key itself, in id order ----
+    const int per = (V + NT - 1) / NT;
+    const int lo = threadIdx.x * per, hi = min(V, lo + per);
+    int my_equal = 0;
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t key = order_key(row[i]);
+        if (key > kth) {
+            const int slot = atomicAdd(&n_gt, 1);
+            cand_key[slot] = key;
+            cand_id[slot] = i;
+        } else if (key == kth) {
+            ++my_equal;
+        }
+    }
+    // exclusive scan of my_equal over the threads (threads own ascending runs of ids)
+    int incl = my_equal;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) scan[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = scan[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        scan[lane] = w;                                // inclusive over warps
+    }
+    __syncthreads();
+    int before = incl - my_equal + (warp > 0 ? scan[warp - 1] : 0);
+    const int base = k - n_equal;                      // = number of keys above the k-th
+    if (my_equal > 0 && before < n_equal) {
+        for (int i = lo; i < hi && before < n_equal; ++i) {
+            if (order_key(row[i]) == kth) {
+                cand_key[base + before] = kth;
+                cand_id[base + before] = i;
+                ++before;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- sort the k candidates: key descending, id ascending ----
+    if (threadIdx.x < k) {
+        const uint32_t key = cand_key[threadIdx.x];
+        const int id = cand_id[threadIdx.x];
+        int rank = 0;
+        for (int j = 0; j < k; ++j) rank += (cand_key[j] > key || (cand_key[j] == key && cand_id[j] < id)) ? 1 : 0;
+        sorted_id[rank] = id;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    // ---- the reference's loops over the sorted candidates ----
+    auto logit_of = [&](int j) { return row[sorted_id[j]] + 0.0f; };
+    int n = k;
+    if (prm.top_p < 1.0f) {
+        const float mx = logit_of(0);
+        double z = 0.0;
+        for (int j = 0; j < n; ++j) z += exp((double)logit_of(j) - (double)mx);
+        double cum = 0.0;
+        int keep = n;
+        for (int j = 0; j < n; ++j) {
+            cum += exp((double)logit_of(j) - (double)mx);
+            if (cum >= (double)prm.top_p * z) { keep = j + 1; break; }
+        }
+        n = keep;
+    }
+    // min-p: the candidates are sorted, so the survivors are a prefix
+    {
+        const float cut = logit_of(0) + prm.log_min_p;
+        int keep = 0;
+        for (int j = 0; j < n; ++j)
+            if (!(logit_of(j) < cut)) ++keep; else break;
+        n = keep > 0 ? keep : 1;
+    }
+    const float mx = logit_of(0);
+    double z = 0.0;
+    for (int j = 0; j < n; ++j) z += (double)(float)exp((double)(logit_of(j) - mx) / (double)prm.temperature);
+    const double r = prm.uniform * z;
+    double cum = 0.0;
+    int pick = sorted_id[n - 1];
+    for (int j = 0; j < n; ++j) {
+        cum += (double)(float)exp((double)(logit_of(j) - mx) / (double)prm.temperature);
+        if (r < cum) { pick = sorted_id[j]; break; }
+    }
+    out[blockIdx.x] = pick;
+}
+
 }  // namespace
 
 PH_EXPORT int ph_argmax(const float* logits, int R, int V, int32_t* out, cudaStream_t stream) {
@@ -133,3 +287,15 @@ PH_EXPORT int ph_sample_temperature(const float* logits, int R, int V, const flo
     sample_temperature_kernel<<<R, NT, 0, stream>>>(logits, V, temperature, uniform, range, out);
     return check_launch("sample_temperature");
 }
+
+// rows: R records {double uniform; float top_p, log_min_p, temperature; int top_k} (24 bytes each) on the device.
+// top_k of 1 .. 256 per row; temperature > 0.
+PH_EXPORT int ph_sample_chain(const float* logits, int R, int V, const void* rows, int32_t* out, cudaStream_t stream) {
+    if (!logits || !out || !rows || R < 0 || V < 1) return fail(PH_ERR_ARG, "sample_chain: bad arguments (rows %d, V %d)", R, V);
+    static_assert(sizeof(ChainRow) == 24, "the host packs 24-byte records");
+    if (R == 0) return PH_OK;
+    sample_chain_kernel<<<R, NT, 0, stream>>>(logits, V, (const ChainRow*)rows, out);
+    return check_launch("sample_chain");
+}
+
+PH_EXPORT int ph_sample_chain_max_k(void) { return KMAX; }

@@ -359,9 +359,10 @@ class Engine:
 
     # ---- sampling --------------------------------------------------------------------------------
     def sample(self, logits: torch.Tensor, samplers) -> List[int]:
-        """One token per row of ``logits`` with the row's sampler.  Greedy and plain temperature sampling run
-        in the device kernels (the uniform number still comes from the sampler's generator, one per token);
-        every other chain runs on the host over a copy of the row."""
+        """One token per row of ``logits`` with the row's sampler.  Greedy, plain temperature sampling and the
+        chain with top-k on run in the device kernels (the uniform number still comes from the sampler's
+        generator, one per token); penalties, and top-p or min-p without top-k, run on the host over a copy of
+        the row."""
         from ..csrc import ops
         R = len(samplers)
         if logits is None or logits.shape[0] != R:
@@ -386,6 +387,18 @@ class Engine:
             for i, m in enumerate(modes):
                 if m == "temperature":
                     out[i] = host[i]
+        if "chain" in modes:
+            import numpy as np
+            which = [i for i, m in enumerate(modes) if m == "chain"]
+            rec = np.zeros(len(which), dtype=ops.CHAIN_ROW)
+            for j, i in enumerate(which):
+                rec[j] = samplers[i].chain_record()
+            rows = torch.from_numpy(rec.view(np.uint8).reshape(len(which), 24)).to(self.device)
+            picked = logits if len(which) == R else logits.index_select(0, torch.tensor(which, device=self.device))
+            ids = self.workspace.get("sample_chain", (len(which),), torch.int32)
+            ops.sample_chain(picked, rows, ids)
+            for i, tok in zip(which, ids.cpu().tolist()):
+                out[i] = tok
         for i, m in enumerate(modes):
             if m is None:
                 out[i] = samplers[i].sample(logits[i].float().cpu().numpy())

@@ -56,8 +56,11 @@ class Sampler:
     def is_greedy(self) -> bool:
         return self.params.temperature <= 0.0 or self.params.top_k == 1
 
+    CHAIN_MAX_K = 256      # most candidates the device's chain kernel keeps
+
     def device_mode(self) -> Optional[str]:
-        """"greedy" or "temperature" when a device kernel gives the same result as the chain, else None."""
+        """"greedy", "temperature" or "chain" (top-k on, at most CHAIN_MAX_K) when a device kernel gives the
+        same result as the chain on the host, else None (penalties, top-p or min-p without top-k)."""
         if self.penalised():
             return None
         if self.is_greedy():
@@ -65,7 +68,16 @@ class Sampler:
         p = self.params
         if p.top_k <= 0 and p.top_p >= 1.0 and p.min_p <= 0.0:
             return "temperature"
+        if 0 < p.top_k <= self.CHAIN_MAX_K:
+            return "chain"
         return None
+
+    def chain_record(self):
+        """(uniform, top_p, log(min_p) or -inf, temperature, top_k) for the device's chain kernel; draws the
+        token's uniform number."""
+        p = self.params
+        log_min_p = float(np.float32(math.log(p.min_p))) if p.min_p > 0.0 else -math.inf      # as sample() rounds it
+        return (self.uniform(), p.top_p, log_min_p, p.temperature, p.top_k)
 
     def uniform(self) -> float:
         return self.rng.uniform()

@@ -532,3 +532,41 @@ def test_qk_norm_rope_of_many_tokens_gives_the_bits_of_few(HQ, HKV, splits, dtyp
     written[slots[slots >= 0].long().cpu()] = True
     untouched = pool_all.float().cpu().permute(0, 4, 1, 2, 3, 5).reshape(n_pages * ps, -1)[~written]
     assert torch.isnan(untouched).all()
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_sample_chain_equals_the_host_chain(V):
+    """top-k -> top-p -> min-p -> temperature -> draw on the device picks the token the host chain picks, for the
+    same uniform number: rows with ties at the k-th place, flat rows, peaked rows, every filter on and off."""
+    import numpy as np
+    from purhie_b200.csrc import ops
+    from purhie_b200.sampling import Sampler, SamplerParams
+    g = torch.Generator().manual_seed(V)
+    cases = []
+    for top_k in (2, 40, 256):
+        for top_p in (0.5, 0.95, 1.0):
+            for min_p in (0.0, 0.05):
+                for temperature in (0.7, 1.3):
+                    cases.append((top_k, top_p, min_p, temperature))
+    R = len(cases)
+    logits = torch.randn(R, V, generator=g) * 3.0
+    logits[1] = torch.round(logits[1])                        # many equal logits: ties at the k-th place and inside
+    logits[2] = 0.25                                          # all equal
+    logits[3, 17] = 40.0                                      # one token has all the mass
+    logits[4] = -logits[4].abs()
+    logits[4, ::7] = -0.0
+    logits[5] = torch.round(logits[5] * 2) / 2
+    dev = logits.to(DEV)
+    for seed in (0, 1, 2):
+        host, device = [], []
+        rec = np.zeros(R, dtype=ops.CHAIN_ROW)
+        for r, (top_k, top_p, min_p, temperature) in enumerate(cases):
+            prm = SamplerParams(temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p, seed=seed * 1000 + r)
+            a, b = Sampler(prm), Sampler(prm)
+            assert b.device_mode() == "chain"
+            host.append(a.sample(logits[r].numpy()))
+            rec[r] = b.chain_record()
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample_chain(dev, torch.from_numpy(rec.view(np.uint8).reshape(R, 24)).to(DEV), out)
+        device = out.cpu().tolist()
+        assert device == host, [(i, cases[i], host[i], device[i]) for i in range(R) if host[i] != device[i]]
