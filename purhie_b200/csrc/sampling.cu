@@ -136,86 +136,216 @@ struct ChainRow {
     int top_k;
 };
 
-__global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restrict__ logits, int V,
-                                                          const ChainRow* __restrict__ rows, int32_t* __restrict__ out) {
-    __shared__ int hist[256];
-    __shared__ uint32_t sel_prefix, sel_mask;
-    __shared__ int sel_remaining, n_gt;
-    __shared__ int scan[NT / 32];
-    __shared__ uint32_t cand_key[KMAX];
-    __shared__ int cand_id[KMAX], sorted_id[KMAX];
-    const float* row = logits + (size_t)blockIdx.x * V;
-    const ChainRow prm = rows[blockIdx.x];
-    const int k = min(min(prm.top_k, V), KMAX);
+constexpr int LIST_MAX = 6144;     // most tokens the chain kernel compacts into shared memory before it selects
+constexpr int CHAIN_SMEM = LIST_MAX * 8;
+
+// Inclusive scan of v over the block's threads in thread order; scratch holds one int per warp.
+__device__ __forceinline__ int block_scan_inclusive(int v, int* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) { sel_prefix = 0; sel_mask = 0; sel_remaining = k; n_gt = 0; }
-    // ---- the key of the k-th best: eight bits at a time, from the top ----
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = scratch[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += u;
+        }
+        scratch[lane] = w;
+    }
+    __syncthreads();
+    return incl + (warp > 0 ? scratch[warp - 1] : 0);
+}
+
+// Warp 0, all lanes: the bin of hist (walking down from 255) in which the remaining-th largest lies; returns the bin
+// and, through taken, how many lie in the bins above it.
+__device__ __forceinline__ int pick_bin(const int* hist, int remaining, int& taken) {
+    const int lane = threadIdx.x & 31;
+    // lane l owns bins 255 - 8 l .. 248 - 8 l, so that lanes ascend as bins descend
+    int c[8], mine = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { c[j] = hist[255 - 8 * lane - j]; mine += c[j]; }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    const unsigned reach = __ballot_sync(0xffffffffu, incl >= remaining);
+    const int owner = reach ? __ffs(reach) - 1 : 31;
+    int bin = 0, above = 0;
+    if (lane == owner) {
+        int acc = incl - mine;
+        int j = 0;
+        for (; j < 7; ++j) {
+            if (acc + c[j] >= remaining) break;
+            acc += c[j];
+        }
+        bin = 255 - 8 * lane - j;
+        above = acc;
+    }
+    bin = __shfl_sync(0xffffffffu, bin, owner);
+    taken = __shfl_sync(0xffffffffu, above, owner);
+    return bin;
+}
+
+// Radix selection, eight bits a pass from the top, of the rank-th largest of the values the callback yields for
+// items 0 .. n-1 (it returns false for items that do not take part).  Returns the value; rank becomes how many items
+// with exactly that value are still to be taken.  All threads call it.
+template <typename Get>
+__device__ __forceinline__ uint32_t radix_select(int n, int& rank, int* hist, uint32_t* sel, Get get) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) { sel[0] = 0; sel[1] = 0; sel[2] = (uint32_t)rank; }
     for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = threadIdx.x; i < 256; i += NT) hist[i] = 0;
         __syncthreads();
-        const uint32_t prefix = sel_prefix, mask = sel_mask;
-        for (int i0 = 0; i0 < V; i0 += NT) {
+        const uint32_t prefix = sel[0], mask = sel[1];
+        for (int i0 = 0; i0 < n; i0 += NT) {
             const int i = i0 + threadIdx.x;
-            const bool in = i < V;
-            const uint32_t key = in ? order_key(row[i]) : 0u;
-            const bool take = in && (key & mask) == prefix;
+            uint32_t key = 0;
+            const bool take = i < n && get(i, key) && (key & mask) == prefix;
             const int bin = take ? (int)((key >> shift) & 255u) : -1;
-            // lanes with the same bin add once
-            const unsigned peers = __match_any_sync(0xffffffffu, bin);
+            const unsigned peers = __match_any_sync(0xffffffffu, bin);          // lanes with the same bin add once
             if (take && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], __popc(peers));
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int acc = 0, b = 255;
-            for (; b > 0; --b) {
-                if (acc + hist[b] >= sel_remaining) break;
-                acc += hist[b];
-            }
-            sel_remaining -= acc;                      // how many to take from bin b (and, in the end, of the key itself)
-            sel_prefix |= (uint32_t)b << shift;
-            sel_mask |= 255u << shift;
+        if (warp == 0) {
+            int taken;
+            const int b = pick_bin(hist, (int)sel[2], taken);
+            __syncwarp();
+            if (lane == 0) { sel[2] -= (uint32_t)taken; sel[0] |= (uint32_t)b << shift; sel[1] |= 255u << shift; }
         }
         __syncthreads();
     }
-    const uint32_t kth = sel_prefix;
-    const int n_equal = sel_remaining;                 // tokens with exactly the k-th key to keep: the lowest ids
-    // ---- collect: everything above the k-th key, then the first n_equal with the key itself, in id order ----
-    const int per = (V + NT - 1) / NT;
-    const int lo = threadIdx.x * per, hi = min(V, lo + per);
-    int my_equal = 0;
-    for (int i = lo; i < hi; ++i) {
-        const uint32_t key = order_key(row[i]);
-        if (key > kth) {
-            const int slot = atomicAdd(&n_gt, 1);
-            cand_key[slot] = key;
-            cand_id[slot] = i;
-        } else if (key == kth) {
-            ++my_equal;
-        }
-    }
-    // exclusive scan of my_equal over the threads (threads own ascending runs of ids)
-    int incl = my_equal;
+    rank = (int)sel[2];
+    return sel[0];
+}
+
+// The k best of a row (logit descending, id ascending) into cand_key / cand_id, in any order.
+//
+// A pass over the row finds the largest logit.  A second pass copies the tokens whose key shares the maximum's top
+// eight bits (positive logits down to half the maximum, at the least) into a list in shared memory; if those are
+// fewer than k the pass is repeated one bin further down, up to three times.  The k best are then selected in the
+// list: by key, and among equal keys at the k-th place by id, lowest first.  A row for which no such list of k to
+// LIST_MAX tokens exists (nearly flat, or spread over many powers of two) is selected from directly, with four
+// passes over the row for the key and a walk in id order for the ties.
+__device__ void select_top_k(const float* __restrict__ row, int V, int k, unsigned char* dyn, uint32_t* cand_key, int* cand_id) {
+    __shared__ int hist[256];
+    __shared__ int scratch[32];
+    __shared__ float warp_max_v[32];
+    __shared__ uint32_t sel[3];
+    __shared__ int n_gt, n_list;
+    uint32_t* list_key = (uint32_t*)dyn;                          // [LIST_MAX]
+    int* list_id = (int*)(list_key + LIST_MAX);                   // [LIST_MAX]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int UNROLL = 8;                                     // loads in flight per thread
+    if (threadIdx.x == 0) n_gt = 0;
+    // ---- the largest logit ----
+    float mx = -INFINITY;
+    for (int i0 = 0; i0 < V; i0 += NT * UNROLL) {
+        float v[UNROLL];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-    }
-    if (lane == 31) scan[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-        int w = scan[lane];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += v;
+        for (int u = 0; u < UNROLL; ++u) {
+            const int i = i0 + u * NT + threadIdx.x;
+            v[u] = i < V ? row[i] : -INFINITY;
         }
-        scan[lane] = w;                                // inclusive over warps
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) mx = fmaxf(mx, v[u]);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) warp_max_v[warp] = mx;
+    __syncthreads();
+    mx = warp_max(warp_max_v[lane]);
+    const int b_max = (int)(order_key(mx) >> 24);
+    // ---- the tokens near the maximum into the list ----
+    bool listed = false;
+    for (int j = 0; j < 4 && b_max - j >= 0 && !listed; ++j) {
+        const uint32_t key_lo = (uint32_t)(b_max - j) << 24;      // the smallest key of the bin
+        const float t = key_lo == 0 ? -INFINITY : __uint_as_float((key_lo & 0x80000000u) ? (key_lo & 0x7fffffffu) : ~key_lo);
+        __syncthreads();
+        if (threadIdx.x == 0) n_list = 0;
+        __syncthreads();
+        for (int i0 = 0; i0 < V; i0 += NT * UNROLL) {
+            float v[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = i0 + u * NT + threadIdx.x;
+                v[u] = i < V ? row[i] : -INFINITY;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int i = i0 + u * NT + threadIdx.x;
+                const bool take = i < V && v[u] >= t;
+                const unsigned m = __ballot_sync(0xffffffffu, take);
+                if (m) {                                           // rare: one shared counter, bumped once per warp
+                    int base = 0;
+                    if (lane == 0) base = atomicAdd(&n_list, __popc(m));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    const int slot = base + __popc(m & ((1u << lane) - 1u));
+                    if (take && slot < LIST_MAX) { list_key[slot] = order_key(v[u]); list_id[slot] = i; }
+                }
+            }
+        }
+        __syncthreads();
+        if (n_list > LIST_MAX) break;                              // the bins further down hold more still
+        listed = n_list >= k;
     }
     __syncthreads();
-    int before = incl - my_equal + (warp > 0 ? scan[warp - 1] : 0);
-    const int base = k - n_equal;                      // = number of keys above the k-th
-    if (my_equal > 0 && before < n_equal) {
-        for (int i = lo; i < hi && before < n_equal; ++i) {
+    if (listed) {
+        const int n = n_list;
+        int n_equal = k;
+        const uint32_t kth = radix_select(n, n_equal, hist, sel, [&](int i, uint32_t& key) { key = list_key[i]; return true; });
+        // how many share the k-th key; if more than are wanted, the wanted ones are those with the lowest ids
+        int mine = 0;
+        for (int i = threadIdx.x; i < n; i += NT) mine += list_key[i] == kth;
+        if (threadIdx.x == 0) scratch[0] = 0;
+        __syncthreads();
+        if (mine) atomicAdd(&scratch[0], mine);
+        __syncthreads();
+        const int same = scratch[0];
+        __syncthreads();
+        uint32_t id_cut = 0xffffffffu;                             // ids up to this one are taken among the equal keys
+        if (same > n_equal) {
+            // the n_equal-th smallest id = the (same - n_equal + 1)-th largest
+            int rank = same - n_equal + 1;
+            id_cut = radix_select(n, rank, hist, sel, [&](int i, uint32_t& key) { key = (uint32_t)list_id[i]; return list_key[i] == kth; });
+        }
+        for (int i = threadIdx.x; i < n; i += NT) {
+            const uint32_t key = list_key[i];
+            if (key > kth || (key == kth && (uint32_t)list_id[i] <= id_cut)) {
+                const int slot = atomicAdd(&n_gt, 1);
+                cand_key[slot] = key;
+                cand_id[slot] = list_id[i];
+            }
+        }
+    } else {
+        // ---- selection over the row itself ----
+        int n_equal = k;
+        const uint32_t kth = radix_select(V, n_equal, hist, sel, [&](int i, uint32_t& key) { key = order_key(row[i]); return true; });
+        // threads own ascending runs of ids, so a prefix over threads is a prefix over ids
+        const int per = (V + NT - 1) / NT;
+        const int lo = threadIdx.x * per, hi = min(V, lo + per);
+        int my_equal = 0;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(row[i]);
+            if (key > kth) {
+                const int slot = atomicAdd(&n_gt, 1);
+                cand_key[slot] = key;
+                cand_id[slot] = i;
+            } else if (key == kth) {
+                ++my_equal;
+            }
+        }
+        int before = block_scan_inclusive(my_equal, scratch) - my_equal;
+        const int base = k - n_equal;
+        for (int i = lo; i < hi && my_equal > 0 && before < n_equal; ++i) {
             if (order_key(row[i]) == kth) {
                 cand_key[base + before] = kth;
                 cand_id[base + before] = i;
@@ -224,6 +354,20 @@ __global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restric
         }
     }
     __syncthreads();
+}
+
+__global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restrict__ logits, int V,
+                                                          const ChainRow* __restrict__ rows, int32_t* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char dyn[];
+    __shared__ uint32_t cand_key[KMAX];
+    __shared__ int cand_id[KMAX], sorted_id[KMAX];
+    __shared__ float sorted_logit[KMAX];
+    __shared__ double e_top_p[KMAX];
+    __shared__ float e_draw[KMAX];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    const ChainRow prm = rows[blockIdx.x];
+    const int k = min(min(prm.top_k, V), KMAX);
+    select_top_k(row, V, k, dyn, cand_key, cand_id);
     // ---- sort the k candidates: key descending, id ascending ----
     if (threadIdx.x < k) {
         const uint32_t key = cand_key[threadIdx.x];
@@ -231,40 +375,44 @@ __global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restric
         int rank = 0;
         for (int j = 0; j < k; ++j) rank += (cand_key[j] > key || (cand_key[j] == key && cand_id[j] < id)) ? 1 : 0;
         sorted_id[rank] = id;
+        sorted_logit[rank] = row[id] + 0.0f;
+    }
+    __syncthreads();
+    // the exponentials of the reference's loops, one per thread; the sums stay with one thread, in its order
+    if (threadIdx.x < k) {
+        const float mx = sorted_logit[0];
+        e_top_p[threadIdx.x] = exp((double)sorted_logit[threadIdx.x] - (double)mx);
+        e_draw[threadIdx.x] = (float)exp((double)(sorted_logit[threadIdx.x] - mx) / (double)prm.temperature);
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
-    // ---- the reference's loops over the sorted candidates ----
-    auto logit_of = [&](int j) { return row[sorted_id[j]] + 0.0f; };
     int n = k;
     if (prm.top_p < 1.0f) {
-        const float mx = logit_of(0);
         double z = 0.0;
-        for (int j = 0; j < n; ++j) z += exp((double)logit_of(j) - (double)mx);
+        for (int j = 0; j < n; ++j) z += e_top_p[j];
         double cum = 0.0;
         int keep = n;
         for (int j = 0; j < n; ++j) {
-            cum += exp((double)logit_of(j) - (double)mx);
+            cum += e_top_p[j];
             if (cum >= (double)prm.top_p * z) { keep = j + 1; break; }
         }
         n = keep;
     }
-    // min-p: the candidates are sorted, so the survivors are a prefix
     {
-        const float cut = logit_of(0) + prm.log_min_p;
+        // min-p: the candidates are sorted, so the survivors are a prefix
+        const float cut = sorted_logit[0] + prm.log_min_p;
         int keep = 0;
         for (int j = 0; j < n; ++j)
-            if (!(logit_of(j) < cut)) ++keep; else break;
+            if (!(sorted_logit[j] < cut)) ++keep; else break;
         n = keep > 0 ? keep : 1;
     }
-    const float mx = logit_of(0);
     double z = 0.0;
-    for (int j = 0; j < n; ++j) z += (double)(float)exp((double)(logit_of(j) - mx) / (double)prm.temperature);
+    for (int j = 0; j < n; ++j) z += (double)e_draw[j];
     const double r = prm.uniform * z;
     double cum = 0.0;
     int pick = sorted_id[n - 1];
     for (int j = 0; j < n; ++j) {
-        cum += (double)(float)exp((double)(logit_of(j) - mx) / (double)prm.temperature);
+        cum += (double)e_draw[j];
         if (r < cum) { pick = sorted_id[j]; break; }
     }
     out[blockIdx.x] = pick;
@@ -294,7 +442,13 @@ PH_EXPORT int ph_sample_chain(const float* logits, int R, int V, const void* row
     if (!logits || !out || !rows || R < 0 || V < 1) return fail(PH_ERR_ARG, "sample_chain: bad arguments (rows %d, V %d)", R, V);
     static_assert(sizeof(ChainRow) == 24, "the host packs 24-byte records");
     if (R == 0) return PH_OK;
-    sample_chain_kernel<<<R, NT, 0, stream>>>(logits, V, (const ChainRow*)rows, out);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(sample_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CHAIN_SMEM) != cudaSuccess)
+            return fail(PH_ERR_LAUNCH, "sample_chain: cannot reserve %d bytes of shared memory", CHAIN_SMEM);
+        configured = true;
+    }
+    sample_chain_kernel<<<R, NT, CHAIN_SMEM, stream>>>(logits, V, (const ChainRow*)rows, out);
     return check_launch("sample_chain");
 }
 
