@@ -225,16 +225,15 @@ def main():
         seq = model.seq_new()
         model.seq_select(seq)
         streams.append(model.stream_begin(ids(PREFIX), opts))
-    for _ in range(args.warmup):
-        model.stream_step_batch(streams)
+    model.stream_run(streams, args.warmup)
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     s.record()
-    for _ in range(args.steps):
-        model.stream_step_batch(streams)
+    done = model.stream_run(streams, args.steps)          # host token ids in, every step's sampled ids out
     e.record()
     torch.cuda.synchronize()
+    assert len(done) == args.steps and all(tok is not None for step in done for _, tok in step)
     e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / args.steps
     h2d = eng.last_upload_bytes                                 # the step's packed int32 metadata (ids, positions, tables)
     e2e = {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),

@@ -384,22 +384,32 @@ class Model:
                 results[i] = self._emit(st, int(tok))
         return results
 
-    def _emit(self, st: Stream, tok: int):
+    def _judge(self, st: Stream, tok: int, in_cache: int) -> str:
+        """Take the sampled token: "eog" (not emitted), "stop" (emitted, the stream ends) or "go".  ``in_cache``:
+        tokens of the sequence before this one."""
         o = st.options
         if not o.ignore_eog and tok in self.eos_ids:
             st.done, st.reason = True, STOP_EOG
-            return (False, None)
+            return "eog"
         st.emitted.append(tok)
         st.sampler.accept(tok)
-        st.next_token = tok
         stop = bool(o.on_token(o.user, tok, "", 0)) if o.on_token else False
         if stop:
             st.reason = STOP_CALLBACK
         elif len(st.emitted) >= o.max_new_tokens:
             st.reason = STOP_MAX_TOKENS
-        elif len(self._seqs[st.seq].tokens) + 1 >= self._n_ctx:
+        elif in_cache + 1 >= self._n_ctx:
             st.reason = STOP_CONTEXT_FULL
         else:
+            return "go"
+        return "stop"
+
+    def _emit(self, st: Stream, tok: int):
+        verdict = self._judge(st, tok, len(self._seqs[st.seq].tokens))
+        if verdict == "eog":
+            return (False, None)
+        if verdict == "go":
+            st.next_token = tok
             return (True, tok)
         # every emitted token is decoded into the sequence, so that a later call continues after it
         try:
@@ -409,6 +419,129 @@ class Model:
         st.next_token = None
         st.done = True
         return (False, tok)
+
+    def stream_run(self, streams: Sequence[Stream], n_steps: int):
+        """Up to ``n_steps`` steps of every stream: the list of what :meth:`stream_step_batch` would return step by
+        step (shorter when every stream ends earlier).  While all live streams are decoding and their samplers run
+        on the device, a step is launched with the token ids the step before left on the device, before the host
+        has read them, so the host's work of a step overlaps the device's; the tokens, the stop reasons and the
+        samplers' draws are those of the step-by-step calls, a callback's stop takes effect one step late on the
+        device only (the step that was already running is discarded)."""
+        out = []
+        while len(out) < n_steps and not all(st.done for st in streams):
+            seg = self._run_ahead(streams, n_steps - len(out))
+            if seg:
+                out.extend(seg)
+            else:
+                out.append(self.stream_step_batch(streams))
+        return out
+
+    def _run_ahead(self, streams: Sequence[Stream], max_steps: int):
+        """A run of decode steps each launched before the tokens of the one before are on the host; None when the
+        streams are not all in plain decoding with device samplers, or fewer than two steps are certain to run."""
+        eng = self._need_engine()
+        live = [(i, st) for i, st in enumerate(streams) if not st.done]
+        if not live or any(st.next_token is None or st.pending for _, st in live):
+            return None
+        modes = {st.sampler.device_mode() for _, st in live}
+        if len(modes) != 1 or None in modes:
+            return None
+        seqs = [self._seqs[st.seq] for _, st in live]
+        # steps that cannot end a stream by its token budget or the context: only an end-of-generation token or a
+        # callback may stop a stream inside the run
+        horizon = min(min(st.options.max_new_tokens - len(st.emitted), self._n_ctx - len(s.tokens) - 1)
+                      for (_, st), s in zip(live, seqs))
+        n = min(max_steps, horizon)
+        probe = [StepEntry(("seq", st.seq), [0], [0]) for _, st in live]
+        if n < 2 or not eng.decodes_as_graph(probe):
+            return None
+        # an end-of-generation token is found out after the next step has put it into the cache: it must be possible
+        # to take it back
+        rewindable = not any(g.window is not None for g in eng.cache.groups) and not eng.cache.state_entries
+        if not rewindable and self.eos_ids and any(not st.options.ignore_eog for _, st in live):
+            return None
+        samplers = [st.sampler for _, st in live]
+        results = []
+
+        def settle(toks, fed_logits, own_logits=None):
+            """The tokens sampled by a step (own_logits: its logits) whose successor, if fed_logits (the successor's
+            logits) is given, has already put them into the cache.  Returns the streams' indices in ``live`` that
+            ended."""
+            res = [(False, None)] * len(streams)
+            ended = []
+            for j, ((i, st), s, tok) in enumerate(zip(live, seqs, toks)):
+                tok = int(tok)
+                verdict = self._judge(st, tok, len(s.tokens))
+                if fed_logits is None:                       # not fed yet: as in a step-by-step call
+                    if verdict == "go":
+                        st.next_token = tok
+                        res[i] = (True, tok)
+                    elif verdict == "eog":
+                        res[i] = (False, None)
+                        ended.append(j)
+                    else:
+                        try:
+                            self._feed(st.seq, [tok])
+                        except InferenceError:
+                            pass
+                        st.next_token, st.done = None, True
+                        res[i] = (False, tok)
+                        ended.append(j)
+                    continue
+                if verdict == "eog":
+                    eng.cache.truncate(("seq", st.seq), len(s.tokens))       # the step in flight fed it: take it back
+                    s.logits = own_logits[j]
+                    res[i] = (False, None)
+                    ended.append(j)
+                    continue
+                s.tokens.append(tok)
+                if verdict == "go":
+                    res[i] = (True, tok)
+                else:
+                    s.logits = fed_logits[j]
+                    st.next_token, st.done = None, True
+                    res[i] = (False, tok)
+                    ended.append(j)
+            results.append(res)
+            return ended
+
+        prev = prev_kept = None
+        try:
+            for step in range(n):
+                if step == 0:
+                    entries = [StepEntry(("seq", st.seq), [st.next_token], [0]) for _, st in live]
+                    for (_, st), s in zip(live, seqs):
+                        s.tokens.append(st.next_token)
+                        st.next_token = None
+                else:
+                    entries = probe
+                logits = eng.step(entries, device_tokens=prev.ids if prev is not None else None)
+                snaps = [sm.rng.snapshot() for sm in samplers]
+                pend = eng.sample_async(logits, samplers)
+                kept = logits.clone()                        # the step's logits live in memory the next step reuses
+                if prev is not None:
+                    ended = settle(prev.result(), kept, prev_kept)
+                    if ended:
+                        # what the step in flight sampled for the ended streams is dropped, their draws taken back;
+                        # the others' tokens stand, and the run ends here: the batch has changed
+                        toks = pend.result()
+                        for j in ended:
+                            samplers[j].rng.restore(snaps[j])
+                        keep = [j for j in range(len(live)) if j not in ended]
+                        live_rest = [live[j] for j in keep]
+                        if live_rest:
+                            live, seqs = live_rest, [seqs[j] for j in keep]
+                            for s, j in zip(seqs, keep):
+                                s.logits = kept[j]
+                            settle([toks[j] for j in keep], None)
+                        return results
+                prev, prev_kept = pend, kept
+            for j, s in enumerate(seqs):
+                s.logits = prev_kept[j]
+            settle(prev.result(), None)
+        except OutOfPages as e:
+            raise InferenceError(ERR_CONTEXT_FULL, str(e)) from e
+        return results
 
     # ---- many prompts at once ------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0, seed: int = 0,

@@ -82,6 +82,23 @@ class _DecodeGraph:
     launches: int = 0
 
 
+class PendingTokens:
+    """Tokens being sampled on the device: ``ids`` (int32 on the device, valid in stream order at once) and their
+    copy to pinned host memory, complete when ``event`` is."""
+
+    def __init__(self, capacity: int):
+        self.capacity = capacity
+        self.host = torch.empty(capacity, dtype=torch.int32).pin_memory()
+        self.params = torch.empty(24 * capacity, dtype=torch.uint8).pin_memory()
+        self.event = torch.cuda.Event()
+        self.ids: Optional[torch.Tensor] = None
+        self.rows = 0
+
+    def result(self) -> List[int]:
+        self.event.synchronize()
+        return self.host[:self.rows].tolist()
+
+
 class Engine:
     def __init__(self, model: DecoderModel, config: Optional[ModelConfig], *, page_size: int = 16,
                  max_tokens: int = 4096, max_requests: int = 4, num_pages=None, device="cuda:0",
@@ -109,6 +126,8 @@ class Engine:
         self.max_position = model.spec.max_position
         self.last_stats = StepStats()
         self._meta_host = [(None, None), (None, None)]
+        self._pending_ring: List[Optional[PendingTokens]] = [None] * 4
+        self._pending_turn = 0
         self._meta_turn = 0
         self.cuda_graphs = cuda_graphs
         self.max_graph_batch = max_graph_batch
@@ -280,18 +299,24 @@ class Engine:
         ctx, want_rows = self._context(lay, dev, self.workspace)
         return ctx, want_rows, lay.n_want
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted places, vocab] on the device in the order of the
         entries and of each entry's ``want`` (None when nothing is wanted); they live in scratch memory that
         the next step reuses.  Raises :class:`OutOfPages`, leaving everything as it was, when the cache
-        cannot hold the batch."""
+        cannot hold the batch.
+
+        ``device_tokens`` (int32 on the device, one per entry): a batch of single tokens takes its token ids from
+        there instead of from the entries, whose ids are then placeholders.  That lets a caller launch a step
+        with the tokens the step before sampled without waiting for them (:meth:`sample_async`)."""
         entries = list(entries)
         if not entries:
             return None
         self._validate(entries)
-        if self.cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
-            logits, T, n_want = self._decode_with_graph(entries)
+        if self.decodes_as_graph(entries):
+            logits, T, n_want = self._decode_with_graph(entries, device_tokens)
             q_lens = [1] * T
+        elif device_tokens is not None:
+            raise StepError("token ids from the device need a batch of single tokens that runs as a graph")
         else:
             ctx, want_rows, n_want = self.build_context(entries)
             logits = self.model.forward(ctx, self.views, want_rows, n_want)
@@ -304,7 +329,10 @@ class Engine:
         return logits
 
     # ---- decoding through CUDA graphs --------------------------------------------------------------
-    def _decode_with_graph(self, entries: Sequence[StepEntry]):
+    def decodes_as_graph(self, entries: Sequence[StepEntry]) -> bool:
+        return self.cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries)
+
+    def _decode_with_graph(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None):
         """A batch of single tokens: the launches of the whole model are captured once per (batch size, block
         table width, attention splits) and replayed.  Each graph owns its scratch memory and metadata buffer,
         so nothing it points at ever moves."""
@@ -328,6 +356,8 @@ class Engine:
             g = _DecodeGraph(Workspace(self.device), torch.empty(len(lay.flat), dtype=torch.int32, device=self.device))
             self._graphs[key] = g
         self._upload(lay.flat, g.meta)
+        if device_tokens is not None:
+            g.meta[:S].copy_(device_tokens[:S], non_blocking=True)        # the token ids lead the metadata
         # every row's logits are computed; the wanted ones are picked afterwards
         all_rows = torch.arange(S, dtype=torch.int32, device=self.device) if g.rows is None else g.rows
         g.rows = all_rows
@@ -358,6 +388,53 @@ class Engine:
         return g.logits.index_select(0, idx), S, len(want)
 
     # ---- sampling --------------------------------------------------------------------------------
+    def sample_async(self, logits: torch.Tensor, samplers) -> Optional["PendingTokens"]:
+        """Start sampling one token per row on the device and their copy to the host without waiting for either.
+        Returns None when the rows' samplers do not all run the same device kernel (see :meth:`sample`).  Each
+        sampler draws its uniform number now."""
+        import numpy as np
+        from ..csrc import ops
+        R = len(samplers)
+        if logits is None or logits.shape[0] != R:
+            raise StepError(f"{R} samplers for {0 if logits is None else logits.shape[0]} rows of logits")
+        modes = {s.device_mode() for s in samplers}
+        if len(modes) != 1 or None in modes:
+            return None
+        mode = modes.pop()
+        self._pending_turn = (self._pending_turn + 1) % len(self._pending_ring)
+        slot = self._pending_ring[self._pending_turn]
+        if slot is None or slot.capacity < R:
+            slot = PendingTokens(max(R, 64))
+            self._pending_ring[self._pending_turn] = slot
+        else:
+            slot.event.synchronize()                  # its last copies are done: the pinned buffers may be rewritten
+        ids = torch.empty(R, dtype=torch.int32, device=self.device)
+        if mode == "greedy":
+            ops.argmax(logits, ids)
+        else:
+            rec = slot.params.numpy()[:24 * R].view(ops.CHAIN_ROW)
+            if mode == "chain":
+                for j, s in enumerate(samplers):
+                    rec[j] = s.chain_record()
+                rows = self.workspace.get("sample_rows", (R, 24), torch.uint8)
+                rows.view(-1).copy_(slot.params[:24 * R], non_blocking=True)
+                ops.sample_chain(logits, rows, ids)
+            else:
+                for j, s in enumerate(samplers):
+                    rec[j] = (s.uniform(), 1.0, 0.0, s.params.temperature, 0)
+                rows = self.workspace.get("sample_rows", (R, 24), torch.uint8)
+                rows.view(-1).copy_(slot.params[:24 * R], non_blocking=True)
+                packed = rows.view(-1)
+                temps = self.workspace.get("sample_temps", (R,), torch.float32)
+                unis = self.workspace.get("sample_unis", (R,), torch.float64)
+                unis.copy_(packed.view(torch.float64).view(R, 3)[:, 0])
+                temps.copy_(packed.view(torch.float32).view(R, 6)[:, 4])
+                ops.sample_temperature(logits, temps, unis, ids)
+        slot.host[:R].copy_(ids, non_blocking=True)
+        slot.event.record()
+        slot.ids, slot.rows = ids, R
+        return slot
+
     def sample(self, logits: torch.Tensor, samplers) -> List[int]:
         """One token per row of ``logits`` with the row's sampler.  Greedy, plain temperature sampling and the
         chain with top-k on run in the device kernels (the uniform number still comes from the sampler's

@@ -44,3 +44,14 @@ class MT19937_64:
     def uniform(self) -> float:
         """[0, 1) from the 53 high bits."""
         return (self.next_u64() >> 11) * (1.0 / 9007199254740992.0)
+
+    def snapshot(self):
+        """What :meth:`restore` needs to take back the draws made after this point.  Cheap unless the next draw
+        regenerates the state."""
+        return (self._i, list(self._mt) if self._i >= _NN else None)
+
+    def restore(self, snap) -> None:
+        i, mt = snap
+        if mt is not None:
+            self._mt = mt
+        self._i = i

@@ -106,6 +106,60 @@ def test_temperature_sampling_is_seeded_and_follows_the_host_chain(models):
     assert toks[len(prompt):] == d
 
 
+@pytest.mark.parametrize("sampler", ["greedy", "chain", "temperature"])
+def test_running_ahead_gives_the_tokens_the_stops_and_the_draws_of_single_steps(models, sampler):
+    """stream_run launches a step with the token ids the step before left on the device.  Compared with the
+    same streams stepped one call at a time: equal tokens step by step, equal stop reasons, equal sequences, and
+    samplers that go on with equal draws; streams end by their budget at different steps, by an end-of-generation
+    token (found out one step late: the token is taken back out of the cache) and by a callback."""
+    from purhie_b200.api import GenOptions, load_model
+    from purhie_b200.sampling import SamplerParams
+    folder, cfg, pc, pw = models["A"]
+    prompts = [random_tokens(n, cfg.vocab_size, 90 + i) for i, n in enumerate((3, 21, 9, 30))]
+    budgets = [7, 30, 30, 12]
+
+    def params(i):
+        if sampler == "greedy":
+            return SamplerParams.greedy()
+        if sampler == "temperature":
+            return SamplerParams.pure_temperature(0.9, seed=i + 1)
+        return SamplerParams(temperature=0.9, top_k=5, top_p=0.9, min_p=0.02, seed=i + 1)
+
+    def run(ahead, eos):
+        model = load_model(folder, dtype="float32")
+        model.kv_cache_init(cfg.max_position_embeddings, max_sequences=4, page_size=TINY["A"][1]["page_size"])
+        model.eos_ids = eos
+        streams = []
+        for i, (p, b) in enumerate(zip(prompts, budgets)):
+            stop_at = (lambda user, tok, text, n, seen=[]: (seen.append(tok), len(seen) >= 9)[1]) if i == 2 else None
+            opts = GenOptions(sampler=params(i), max_new_tokens=b, ignore_eog=(i == 1), on_token=stop_at)
+            model.seq_select(model.seq_new() if i else 0)
+            streams.append(model.stream_begin(p, opts))
+        if ahead:
+            steps = model.stream_run(streams, 40)
+        else:
+            steps = []
+            while not all(st.done for st in streams):
+                steps.append(model.stream_step_batch(streams))
+        tail = [st.sampler.uniform() for st in streams]
+        seqs = [list(model._seqs[st.seq].tokens) for st in streams]
+        lengths = [model.engine.length(("seq", st.seq)) for st in streams]
+        logits = [model._seqs[st.seq].logits.clone() for st in streams]
+        return steps, [st.emitted for st in streams], [st.reason for st in streams], tail, seqs, lengths, logits
+
+    # no end-of-generation ids first, then one that the longest stream is known to produce on the way
+    base = run(False, [])
+    eos = [base[1][3][5]]
+    for eos_ids in ([], eos):
+        a, b = run(False, eos_ids), run(True, eos_ids)
+        assert a[0] == b[0] and a[1] == b[1] and a[2] == b[2]
+        assert a[3] == b[3]                                  # the generators stand where they would
+        assert a[4] == b[4] and a[5] == b[5]
+        for x, y in zip(a[6], b[6]):
+            assert torch.equal(x, y)
+    assert any(len(set(r)) > 1 for r in [base[2]])           # the streams did end for different reasons
+
+
 def test_prefix_reuse_context_full_and_errors(models):
     from purhie_b200.api import ERR_CONTEXT_FULL, ERR_INVALID_STATE, GenOptions, InferenceError, load_model
     from purhie_b200.sampling import SamplerParams
