@@ -300,10 +300,9 @@ class Model:
         else:
             self.last_prompt_stats = (0, len(prompt))
         st = Stream(self, self._current, prompt, opts)
-        while True:
-            going, tok = self.stream_step(st)
-            if not going:
-                return st.emitted, st.reason
+        while not st.done:
+            self.stream_run([st], 1 << 20)
+        return st.emitted, st.reason
 
     def stream_begin(self, prompt_ids: Sequence[int], options: Optional[GenOptions] = None) -> Stream:
         opts = options or gen_default_options()
