@@ -77,6 +77,7 @@ class Scheduler:
         """``engine`` offers ``cache`` (a :class:`CacheManager`), ``step(entries)`` and ``sample(logits,
         samplers)``, as :class:`purhie_b200.engine.Engine` does."""
         self.engine = engine
+        self.run_ahead = True                       # decode_ahead() may launch steps before the tokens of the last are read
         self.cache = engine.cache
         self.max_batch_tokens = max_batch_tokens
         self.prefill_chunk = prefill_chunk
@@ -267,8 +268,63 @@ class Scheduler:
         self._finish(r, reason)
         return StepEvent(r.request_id, tok, True, reason)
 
+    def decode_ahead(self, max_steps: int = 1 << 30) -> int:
+        """While nothing waits and every running request is decoding with a device sampler: decode steps each
+        launched with the token ids the step before left on the device, the host reading them one step behind.
+        The run ends when a request finishes (what the step in flight sampled for it is dropped; its pages are
+        given back as for any finished request, and are not handed out again before a later step is launched
+        behind the one in flight), when pages run out (the ordinary step then decides whom to preempt) or at the
+        step before the first request's token budget or the context could end it.  Returns the number of steps
+        run; 0: not applicable, take an ordinary step."""
+        from .engine import StepEntry
+        from ..cache.pages import OutOfPages
+        run = list(self.running)
+        as_graph = getattr(self.engine, "decodes_as_graph", None)
+        if not self.run_ahead or as_graph is None or self.waiting or not run or len(run) > self.max_batch_tokens:
+            return 0
+        if any(len(r.tokens()) - self._computed(r) != 1 or not r.output for r in run):
+            return 0
+        modes = {r.sampler.device_mode() for r in run}
+        if len(modes) != 1 or None in modes:
+            return 0
+        probe = [StepEntry(r.request_id, [0], [0]) for r in run]
+        horizon = min(min(r.max_new_tokens - len(r.output), self.n_ctx - len(r.tokens())) for r in run)
+        n = min(max_steps, horizon)
+        if n < 2 or not as_graph(probe):
+            return 0
+        samplers = [r.sampler for r in run]
+        prev, done = None, 0
+
+        def settle(toks) -> bool:
+            ended = False
+            for r, tok in zip(run, toks):
+                ended |= self._emit(r, int(tok)).finished
+            return ended
+
+        for step in range(n):
+            entries = [StepEntry(r.request_id, [r.output[-1]], [0]) for r in run] if step == 0 else probe
+            try:
+                logits = self.engine.step(entries, device_tokens=prev.ids if prev is not None else None)
+            except OutOfPages:
+                break
+            self.steps += 1
+            done += 1
+            pend = self.engine.sample_async(logits, samplers)
+            if prev is not None and settle(prev.result()):
+                # the batch changes: the step in flight stands for the requests that go on
+                toks = pend.result()
+                for r, tok in zip(run, toks):
+                    if r.status == "running":
+                        self._emit(r, int(tok))
+                return done
+            prev = pend
+        if prev is not None:
+            settle(prev.result())
+        return done
+
     def run(self) -> Dict[object, Request]:
         """Step until nothing is waiting or running."""
         while self.has_work():
-            self.step()
+            if not self.decode_ahead():
+                self.step()
         return self.finished

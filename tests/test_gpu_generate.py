@@ -160,6 +160,38 @@ def test_running_ahead_gives_the_tokens_the_stops_and_the_draws_of_single_steps(
     assert any(len(set(r)) > 1 for r in [base[2]])           # the streams did end for different reasons
 
 
+def test_scheduler_running_ahead_changes_no_token(models):
+    """The scheduler's decode phase launches steps with the ids the step before left on the device; requests of
+    different budgets, a seeded chain sampler, an end-of-generation id on the way: the same outputs and stop reasons
+    as with every step read before the next is launched."""
+    from purhie_b200.api import load_model
+    from purhie_b200.engine.scheduler import Request, Scheduler
+    from purhie_b200.sampling import SamplerParams
+    folder, cfg, pc, pw = models["B"]
+    prompts = [random_tokens(n, cfg.vocab_size, 120 + i) for i, n in enumerate((5, 33, 18, 2))]
+    budgets = [6, 25, 14, 25]
+
+    def run(ahead, eos):
+        model = load_model(folder, dtype="float32")
+        model.kv_cache_init(256, max_sequences=4, page_size=8)
+        eng = model.engine
+        eng.release(("seq", 0))
+        sched = Scheduler(eng, max_batch_tokens=64, prefill_chunk=16, n_ctx=256)
+        sched.run_ahead = ahead
+        for i, (p, b) in enumerate(zip(prompts, budgets)):
+            sp = SamplerParams(temperature=0.8, top_k=6, top_p=0.9, min_p=0.01, seed=40 + i)
+            sched.add(Request(("r", i), list(p), sp, b, eos, False))
+        done = sched.run()
+        return [(done[("r", i)].output, done[("r", i)].stop_reason) for i in range(4)], sched.steps
+
+    base, _ = run(False, [])
+    for eos in ([], [base[1][0][9]]):
+        a, steps_a = run(False, eos)
+        b, steps_b = run(True, eos)
+        assert a == b
+        assert steps_b <= steps_a + 2                        # at most the step in flight when a request ended is extra
+
+
 def test_prefix_reuse_context_full_and_errors(models):
     from purhie_b200.api import ERR_CONTEXT_FULL, ERR_INVALID_STATE, GenOptions, InferenceError, load_model
     from purhie_b200.sampling import SamplerParams

@@ -122,7 +122,14 @@ def test_temperature_distribution():
     for _ in range(n):
         counts[s.sample(l)] += 1
     assert np.abs(counts / n - p).max() < 0.012
-    assert s.device_mode() == "temperature" and Sampler(SamplerParams()).device_mode() is None
+    # which kernel samples what: plain temperature, the chain with top-k on; the host keeps top-p without top-k,
+    # more candidates than the kernel holds, and penalties
+    assert s.device_mode() == "temperature" and Sampler(SamplerParams()).device_mode() == "chain"
+    assert Sampler(SamplerParams(top_k=0)).device_mode() is None
+    assert Sampler(SamplerParams(top_k=Sampler.CHAIN_MAX_K + 1)).device_mode() is None
+    pen = Sampler(SamplerParams(repeat_penalty=1.1))
+    pen.accept(3)
+    assert pen.device_mode() is None and Sampler(SamplerParams(temperature=0.0)).device_mode() == "greedy"
     assert Sampler(SamplerParams.greedy()).device_mode() == "greedy"
 
 
