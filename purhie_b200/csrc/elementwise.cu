@@ -79,6 +79,9 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
+// Partial sums of a split product fetched at once (a decode step's o and down products come in nine parts).
+constexpr int PARTS_IN_FLIGHT = 12;
+
 template <typename TA, typename TY, int MAX_IT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
@@ -99,14 +102,14 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
             float4 acc = Vec4<float>::load(xr + i);
             if (add) {
                 const TA* a = add + (size_t)t * E + i;
-                for (int s0 = 0; s0 < add_splits; s0 += 4) {      // four loads in flight, added in order
-                    float4 u[4];
+                for (int s0 = 0; s0 < add_splits; s0 += PARTS_IN_FLIGHT) {      // loads in flight, added in order
+                    float4 u[PARTS_IN_FLIGHT];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                    for (int j = 0; j < PARTS_IN_FLIGHT; ++j)
                         u[j] = s0 + j < add_splits ? Vec4<TA>::load(a + (size_t)(s0 + j) * add_split_stride)
                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                    for (int j = 0; j < PARTS_IN_FLIGHT; ++j)
                         if (s0 + j < add_splits) { acc.x += u[j].x; acc.y += u[j].y; acc.z += u[j].z; acc.w += u[j].w; }
                 }
                 if (write_x) Vec4<float>::store(xr + i, acc);
@@ -167,16 +170,16 @@ __global__ void swiglu_vec_kernel(const TI* __restrict__ gu, int splits, long lo
     if (q >= total4) return;
     const TI* src = gu + q * 8;
     float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b = a;
-    for (int s0 = 0; s0 < splits; s0 += 2) {
-        float4 u[4];
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+        float4 u[8];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 4; ++j) {
             const bool on = s0 + j < splits;
             u[2 * j] = on ? Vec4<TI>::load(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             u[2 * j + 1] = on ? Vec4<TI>::load(src + (size_t)(s0 + j) * split_stride + 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 4; ++j)
             if (s0 + j < splits) {
                 a.x += u[2 * j].x; a.y += u[2 * j].y; a.z += u[2 * j].z; a.w += u[2 * j].w;
                 b.x += u[2 * j + 1].x; b.y += u[2 * j + 1].y; b.z += u[2 * j + 1].z; b.w += u[2 * j + 1].w;

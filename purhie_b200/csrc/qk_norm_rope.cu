@@ -154,13 +154,13 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
         v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (head0 + i >= n_heads) continue;
         const TI* src = qkv + (size_t)t * n_heads * D + (size_t)(head0 + i) * D + d0;
-        for (int s0 = 0; s0 < splits; s0 += 4) {
-            float4 u[4];
+        for (int s0 = 0; s0 < splits; s0 += 8) {             // eight partial sums in flight, added in order
+            float4 u[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 8; ++j)
                 u[j] = s0 + j < splits ? ld4(src + (size_t)(s0 + j) * split_stride) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 8; ++j)
                 if (s0 + j < splits) { v[i].x += u[j].x; v[i].y += u[j].y; v[i].z += u[j].z; v[i].w += u[j].w; }
         }
     }
