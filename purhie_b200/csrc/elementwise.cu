@@ -88,9 +88,17 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                                        const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
     __shared__ float scratch[128];
     pdl_launch_dependents();
-    pdl_wait();
+    // what no kernel of this step writes (the norm's weight, the row list) is fetched while the kernel in front
+    // still runs
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
+    float4 w[MAX_IT];
+#pragma unroll
+    for (int it = 0; it < MAX_IT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        w[it] = weight && i < E ? Vec4<float>::load(weight + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    pdl_wait();
     float* xr = x + (size_t)t * E;
     float4 v[MAX_IT];
     float ss[MAX_IT];
@@ -136,10 +144,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
 #pragma unroll
     for (int it = 0; it < MAX_IT; ++it) {
         const int i = (it * blockDim.x + threadIdx.x) * 4;
-        if (i < E) {
-            const float4 w = Vec4<float>::load(weight + i);
-            Vec4<TY>::store(yr + i, make_float4(v[it].x * inv * w.x, v[it].y * inv * w.y, v[it].z * inv * w.z, v[it].w * inv * w.w));
-        }
+        if (i < E)
+            Vec4<TY>::store(yr + i, make_float4(v[it].x * inv * w[it].x, v[it].y * inv * w[it].y, v[it].z * inv * w[it].z,
+                                                v[it].w * inv * w[it].w));
     }
 }
 

@@ -140,13 +140,26 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
                                          int page_size, int HQ, int HKV) {
     constexpr int D = 128;
     pdl_launch_dependents();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head0 = (blockIdx.y * WARPS + warp) * HPW;      // this warp's HPW consecutive heads of token t
     const int t = blockIdx.x;
     const int n_heads = HQ + 2 * HKV;
     if (head0 >= n_heads) return;
     const int d0 = lane * 4;
+    // what no kernel of this step writes (positions, slots, the table, the norms' weights) is fetched while the
+    // kernel in front still runs
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), sn = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (cos_sin) {
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+        const int j = (lane & 15) * 4;                       // pair index of this lane's first dimension
+        c = ld4(cos_sin + (size_t)pos * D + j);
+        sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
+    }
+    const float4 gq = q_w ? ld4(q_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    const float4 gk = k_w ? ld4(k_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    pdl_wait();
     // every head's loads are issued before any of them is used
     float4 v[HPW];
 #pragma unroll
@@ -163,15 +176,6 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
             for (int j = 0; j < 8; ++j)
                 if (s0 + j < splits) { v[i].x += u[j].x; v[i].y += u[j].y; v[i].z += u[j].z; v[i].w += u[j].w; }
         }
-    }
-    const int slot = slot_mapping ? slot_mapping[t] : -1;
-    float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), sn = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (cos_sin) {
-        int pos = positions[t];
-        pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-        const int j = (lane & 15) * 4;                       // pair index of this lane's first dimension
-        c = ld4(cos_sin + (size_t)pos * D + j);
-        sn = ld4(cos_sin + (size_t)pos * D + 64 + j);
     }
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
@@ -193,7 +197,7 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
         if (w) {
             const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
             const float inv = rsqrtf(ss / (float)D + eps);
-            const float4 g = ld4(w + d0);
+            const float4 g = is_q ? gq : gk;
             x.x = x.x * inv * g.x; x.y = x.y * inv * g.y; x.z = x.z * inv * g.z; x.w = x.w * inv * g.w;
         }
         if (cos_sin) {
