@@ -164,9 +164,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torc
             else:
                 gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
             return Addend(out, 1, activated=True)
-    elif fuse_swiglu and not swapped and splits == 1 and N % 2 == 0:
+    elif fuse_swiglu and N % 2 == 0 and (splits == 1 or swapped):
+        # few tokens: K stays whole, so that the epilogue holds whole sums and can apply the activation; the
+        # weight tiles alone (N / 128 of them) keep the SMs streaming
         out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
-        gemm(x[:M], w, out, swapped=False, block_n=block_n, swiglu=True)
+        gemm(x[:M], w, out, swapped=swapped, block_n=block_n, swiglu=True)
         return Addend(out, 1, activated=True)
     if splits > 1:
         out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)

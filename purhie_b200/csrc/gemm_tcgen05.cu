@@ -258,6 +258,25 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t*
     }
 }
 
+// Swapped orientation with the activation: accumulator row a is output feature a, and gate and up features are
+// neighbours (rows 2i and 2i + 1), so neighbouring lanes hold a pair; the even lane writes out[token, a / 2].
+// Every lane of the warp calls this (the exchange needs them all).
+template <int CH>
+__device__ __forceinline__ void store_chunk_swapped_swiglu(const GemmParams& p, const uint32_t* r, int a, int b0, int c) {
+    const bool writer = (a & 1) == 0 && a + 1 < p.rows_a;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const float mine = __uint_as_float(r[j]);
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+        if (writer && b0 + c + j < p.rows_b) {
+            const float h = mine / (1.0f + __expf(-mine)) * other;
+            const size_t at = (size_t)(b0 + c + j) * p.ld + (size_t)(a >> 1);
+            if (p.out_bf16) ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(h);
+            else ((float*)p.out)[at] = h;
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, TileConfig<BN>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -399,7 +418,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint32_t r[CH];
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
-                store_chunk<CH>(p, r, a, b0, c, split_off);
+                if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
+                else store_chunk<CH>(p, r, a, b0, c, split_off);
             }
             tc_fence_before();
             __syncwarp();
@@ -751,8 +771,9 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     const int kblocks = (K + BK - 1) / BK;
     if (splits < 1 || splits > kblocks) return fail(PH_ERR_ARG, "gemm_tcgen05: %d splits for %d blocks of K", splits, kblocks);
     if (splits > 1 && out_dtype != PH_F32) return fail(PH_ERR_ARG, "gemm_tcgen05: partial results are float32");
-    if (swiglu && (swapped || splits > 1 || (N & 1) || block_n < 32))
-        return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs the plain orientation, one split and an even N");
+    if (swiglu && (splits > 1 || (N & 1) || (!swapped && block_n < 32)))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs one split, an even N and, in the plain orientation, "
+                                "tiles of 32 features or more");
     const void* a = swapped ? w : x;
     const void* b = swapped ? x : w;
     const int rows_a = swapped ? N : M, rows_b = swapped ? M : N;

@@ -156,6 +156,20 @@ def test_gemm_tcgen05_pair_equals_one_cta_kernel():
     assert torch.equal(a, b)                # the same products added in the same order of K
 
 
+@pytest.mark.parametrize("M,N,K,block_n", [(1, 256, 128, 16), (8, 1000, 328, 16), (33, 520, 200, 64), (100, 264, 512, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05_swiglu_epilogue_with_few_tokens(M, N, K, block_n, out_dtype):
+    """Swapped orientation: gate and up features are neighbouring accumulator rows, exchanged between lanes."""
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=19), rnd(N, K, dtype=torch.bfloat16, seed=20, scale=0.2)
+    out = torch.full((M, N // 2), float("nan"), dtype=out_dtype, device=DEV)
+    gemm100.gemm(x, w, out, swapped=True, block_n=block_n, swiglu=True)
+    gemm100.check_errors(DEV)
+    y = x.double() @ w.double().T
+    g, u = y[:, 0::2], y[:, 1::2]
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < (3e-5 if out_dtype == torch.float32 else 6e-3)
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     from purhie_b200.csrc import gemm100
     from purhie_b200.csrc.ops import KernelError
