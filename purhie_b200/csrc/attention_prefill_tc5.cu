@@ -15,6 +15,8 @@
 //             when the row maximum has grown by more than 2^8 since it was set; then the row of O in tensor
 //             memory is rescaled (tcgen05.ld / st).
 // Tensor memory: columns 0-63 scores (then P) of even blocks, 64-191 O, 192-255 scores of odd blocks.
+// A tile's keys may be shared by several CTAs (grid z), for a few tiles late in a long context: each leaves its
+// unnormalised sums, its reference and its row sums in scratch, and a second kernel merges them.
 // A row at absolute position z sees positions max(0, z - window + 1) .. z.  Pages past the tile's last token
 // come from an out-of-range coordinate (zeros), scores of invisible keys are replaced by -inf and value rows
 // after the last token inside its page are zeroed before P V, so unwritten page slots may hold anything.
@@ -68,6 +70,9 @@ struct Tc5Params {
     int HQ, HKV, window;
     float scale_log2;
     int* error_flag;
+    int splits;                    // CTAs that share a tile's keys (grid z); > 1: partial results, merged by a second kernel
+    float* part_o;                 // [T][HQ][splits][D] unnormalised partial outputs
+    float* part_ml;                // [T][HQ][splits][2] the exponent's reference and the sum of each partial
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -209,7 +214,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int z_first = ctx_len - q_len + first, z_last = z_first + n_rows - 1;
     const int lo_tile = p.window > 0 ? max(0, z_first - p.window + 1) : 0;
     const int lo_page = lo_tile - (lo_tile & (p.page_size - 1));
-    const int n_blocks = (z_last - lo_page) / BN + 1;
+    const int tile_blocks = (z_last - lo_page) / BN + 1;          // blocks of 64 keys the tile sees
+    // this CTA's share of them: blocks b_first .. b_first + n_blocks - 1 (none when the tile has fewer blocks than CTAs)
+    const int per_split = (tile_blocks + p.splits - 1) / p.splits;
+    const int b_first = (int)blockIdx.z * per_split;
+    const int n_blocks = max(0, min(tile_blocks, b_first + per_split) - b_first);
     const int g = h / (p.HQ / p.HKV);
 
     if (threadIdx.x == 0) {
@@ -245,7 +254,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int32_t* table = p.block_table + (size_t)seg * p.table_stride;
         const int psh = p.page_shift, ppb = BN >> psh;
         int ok = 1;
-        if (lane == 0) {
+        if (lane == 0 && n_blocks > 0) {
             mb::arrive_expect_tx(q_full, Q_BYTES);
             tma_load_4d(q_tile, &map_q, q_full, 0, row0 + first, 0, h);       // box {64, 128 rows, 2 halves, 1 head}
         }
@@ -261,7 +270,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // lane (page j, half) issues one box
             if (lane < ppb * 2) {
                 const int pj = lane >> 1, half = lane & 1;
-                const int pos = lo_page + b * BN + (pj << psh);
+                const int pos = lo_page + (b_first + b) * BN + (pj << psh);
                 int row = p.total_rows;                       // past the tile's last token: zeros
                 if (pos <= z_last) row = (int)((long long)table[pos >> psh] * p.rows_per_page + (long long)g * p.page_size);
                 unsigned char* dst = (is_v ? v_ring : k_ring) + stage * KV_BYTES + half * HALF_KV + (pj << psh) * 128;
@@ -284,7 +293,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc(BM, BN, 0);      // S = Q K^T: both K-major
             constexpr uint32_t idesc_o = make_idesc(BM, D, 1);       // O += P V: V is MN-major
-            bool ok = mb::wait(q_full, 0, p.error_flag, PH_ERR_WAIT_TC5_MMA);
+            bool ok = n_blocks == 0 || mb::wait(q_full, 0, p.error_flag, PH_ERR_WAIT_TC5_MMA);
             // S of block b + 1 is issued before P V of block b where its keys have landed, so that the softmax of
             // the next block finds its scores ready while the tensor core adds this block to O.  Its buffer in
             // tensor memory held S (and P) of block b - 1, whose P V was issued before: the pipe keeps the order.
@@ -341,7 +350,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         float l = 0.0f;
         bool ok = true;
         for (int b = 0; b < n_blocks && ok; ++b) {
-            const int key0 = lo_page + b * BN;
+            const int key0 = lo_page + (b_first + b) * BN;
             const int stage = stage_of(b);
             if (!mb::wait(&s_full[b & 1], (b >> 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
             tc_fence_after();
@@ -409,7 +418,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     }
                 }
             }
-            if (b == n_blocks - 1) {
+            if (b_first + b == tile_blocks - 1) {
                 // value rows after the tile's last token inside its page may hold anything: zero them
                 if (!mb::wait(&v_full[stage], use_parity(b), p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX)) { ok = false; break; }
                 unsigned char* v_tile = v_ring + stage * KV_BYTES;
@@ -426,7 +435,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (lane == 0) mb::arrive(p_full);
         }
         if (ok && n_blocks > 0) ok = mb::wait(o_full, (n_blocks - 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX);
-        if (ok) {
+        if (ok && p.splits == 1) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + first + r) * p.HQ * D + (size_t)h * D;
@@ -448,6 +457,27 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     }
                 }
             }
+        } else if (ok) {
+            // one of several CTAs on this tile: the unnormalised sums, their reference and the row sums go to scratch
+            tc_fence_after();
+            const size_t slot = ((size_t)(row0 + first + r) * p.HQ + h) * p.splits + blockIdx.z;
+            if (r < n_rows) {
+                p.part_ml[slot * 2] = m_ref;                          // -inf, with a sum of 0, when this CTA saw no key of the row
+                p.part_ml[slot * 2 + 1] = l;
+            }
+            if (n_blocks > 0) {
+                float* dst = p.part_o + slot * D;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t raw[32];
+                    tmem_ld32(tmem_o + lane_addr + c * 32, raw);
+                    tmem_ld_wait();
+                    if (r < n_rows) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *(uint4*)(dst + c * 32 + j) = make_uint4(raw[j], raw[j + 1], raw[j + 2], raw[j + 3]);
+                    }
+                }
+            }
         }
     }
     tc_fence_before();
@@ -456,6 +486,50 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         __syncwarp();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+}
+
+// Merges the partial results of the CTAs that shared a tile's keys: grid (tile, head, groups of four rows), a warp per
+// row, four dimensions per lane, every partial of the row fetched before any is used.  A partial with reference -inf
+// saw no key of the row and is skipped (its output slot was never written).
+constexpr int MERGE_MAX = 16;      // most CTAs per tile
+__global__ void __launch_bounds__(128)
+attention_prefill_tc5_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     const int32_t* __restrict__ seg_start, const int32_t* __restrict__ tile_seg,
+                                     const int32_t* __restrict__ tile_first, __nv_bfloat16* __restrict__ out, int HQ, int splits) {
+    pdl_launch_dependents();
+    const int tile = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = tile_seg[tile], first = tile_first[tile];
+    const int row0 = seg_start[seg], n_rows = min(BM, seg_start[seg + 1] - row0 - first);
+    const int r = blockIdx.z * 4 + warp;
+    pdl_wait();
+    if (r >= n_rows) return;
+    const size_t slot0 = ((size_t)(row0 + first + r) * HQ + h) * splits;
+    float ms[MERGE_MAX], ls[MERGE_MAX];
+    float4 o[MERGE_MAX];
+    float m = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX; ++s) {
+        ms[s] = s < splits ? part_ml[(slot0 + s) * 2] : -INFINITY;
+        ls[s] = s < splits ? part_ml[(slot0 + s) * 2 + 1] : 0.0f;
+        m = fmaxf(m, ms[s]);
+    }
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX; ++s)
+        o[s] = s < splits && ms[s] != -INFINITY ? *(const float4*)(part_o + (slot0 + s) * D + lane * 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float l = 0.0f;
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX; ++s) {
+        if (ms[s] == -INFINITY) continue;
+        const float c = exp2f(ms[s] - m);
+        acc.x += c * o[s].x; acc.y += c * o[s].y; acc.z += c * o[s].z; acc.w += c * o[s].w;
+        l += c * ls[s];
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    uint2 v;
+    v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1;
+    *(uint2*)(out + ((size_t)(row0 + first + r) * HQ + h) * D + lane * 4) = v;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -500,14 +574,17 @@ bool encode(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims
 
 PH_DEFINE_LAST_ERROR(ph_flash5)
 
-// q [T, HQ, 128] bfloat16 -> out [T, HQ * 128].  tile_seg / tile_first: the step's prompt portions cut into tiles
+// q [T, HQ, 128] bfloat16 -> out [T, HQ * 128].  splits > 1: that many CTAs share the keys of every tile and leave
+// partial results in part_o [T][HQ][splits][128] and part_ml [T][HQ][splits][2] (float32), which a second kernel merges;
+// for few tiles that look far back.  tile_seg / tile_first: the step's prompt portions cut into tiles
 // of 128 rows (segment, first row of the tile within the portion).  num_pages: pages of the pool that k_base /
 // v_base belong to.
 PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base, const void* v_base, long long page_stride,
                                        int page_size, int num_pages, const int32_t* block_table, int table_stride,
                                        const int32_t* seg_start, const int32_t* seg_ctx_len, const int32_t* tile_seg,
                                        const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
-                                       int window, float scale, int* error_flag, cudaStream_t stream) {
+                                       int window, float scale, int splits, float* part_o, float* part_ml,
+                                       int* error_flag, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out ||
         !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || !(scale > 0.0f))
         return fail(PH_ERR_ARG, "attention_prefill_tc5: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
@@ -517,6 +594,8 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
     if (page_stride % D || (((uintptr_t)q | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)out) & 15))
         return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: tensors must be 16-byte aligned, pages whole rows");
     if (n_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: %d tiles exceed the grid", n_tiles);
+    if (splits < 1 || splits > MERGE_MAX || (splits > 1 && (!part_o || !part_ml || (((uintptr_t)part_o) & 15))))
+        return fail(PH_ERR_ARG, "attention_prefill_tc5: %d splits need 16-byte aligned scratch for the partial results", splits);
     if (n_tiles == 0) return PH_OK;
     const long long rows_per_page = page_stride / D;
     const long long rows = (long long)(num_pages - 1) * rows_per_page + (long long)HKV * page_size;
@@ -538,12 +617,16 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
     p.block_table = block_table; p.table_stride = table_stride; p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len;
     p.tile_seg = tile_seg; p.tile_first = tile_first; p.n_tiles = n_tiles; p.out = (__nv_bfloat16*)out;
     p.HQ = HQ; p.HKV = HKV; p.window = window; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
+    p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
             return fail(PH_ERR_LAUNCH, "attention_prefill_tc5: cannot reserve %d bytes of shared memory", SMEM_BYTES);
         configured = true;
     }
-    launch_overlapped(attention_prefill_tc5_kernel, dim3(HQ, n_tiles), dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
+    launch_overlapped(attention_prefill_tc5_kernel, dim3(HQ, n_tiles, splits), dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
+    if (splits > 1)
+        launch_overlapped(attention_prefill_tc5_combine_kernel, dim3(n_tiles, HQ, BM / 4), dim3(128), 0, stream,
+                          (const float*)part_o, (const float*)part_ml, seg_start, tile_seg, tile_first, (__nv_bfloat16*)out, HQ, splits);
     return check_launch("attention_prefill_tc5");
 }

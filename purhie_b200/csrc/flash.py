@@ -21,7 +21,7 @@ register_signatures("flash", {
                                  c_float, c_int, c_void_p, c_void_p],
     "ph_attention_prefill_tc5": [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                 c_void_p, c_void_p],
+                                 c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "ph_attention_decode": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                             c_void_p],
@@ -79,13 +79,39 @@ def tc5_supports(head_dim: int, page_size: int) -> bool:
     return head_dim == 128 and page_size in (8, 16)
 
 
+def tc5_splits(n_tiles: int, num_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:
+    """CTAs per tile of the tcgen05 prefill kernel.  The time is about (rounds of the CTAs over two slots per SM) x
+    (blocks of 64 keys per CTA + a few for its start) plus, when tiles are shared, what writing and merging the
+    partial results costs; the count with the least wins.  Many tiles, or tiles that look back over few keys, stay
+    whole; a short portion late in a long context is cut so that its CTAs fill the device once."""
+    span = min(max_ctx, window + 128) if window else max_ctx
+    blocks = max(1, -(-span // 64))
+    ctas = max(1, n_tiles * num_heads)
+    best, best_cost = 1, None
+    for s in range(1, min(16, blocks) + 1):
+        cost = -(-(ctas * s) // (2 * sms)) * (-(-blocks // s) + 4)
+        if s > 1:
+            # the second kernel's launch, and every row's partial results (512 bytes per head and CTA) written and
+            # read back, in units of a block's time
+            cost += 8 + 0.5 * s + 0.024 * ctas * s
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def prefill_tc5(q, n_rows, k_base, v_base, page_stride, page_size, num_pages, block_table, seg_start, seg_ctx_len, tile_seg,
-                tile_first, n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
-    """The tcgen05 prefill kernel (attention_prefill_tc5.cu); tiles of 128 rows."""
+                tile_first, n_tiles, out, *, num_heads, num_kv_heads, head_dim, window, scale, splits: int = 1,
+                workspace=None) -> None:
+    """The tcgen05 prefill kernel (attention_prefill_tc5.cu); tiles of 128 rows, each shared by ``splits`` CTAs."""
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = workspace.get("attn_tile_part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
+        part_ml = workspace.get("attn_tile_part_ml", (n_rows, num_heads, splits, 2), torch.float32)
     call("flash", "ph_attention_prefill_tc5", q.data_ptr(), n_rows, k_base.data_ptr(), v_base.data_ptr(), page_stride,
          page_size, num_pages, block_table.data_ptr(), block_table.shape[-1], seg_start.data_ptr(), seg_ctx_len.data_ptr(),
          tile_seg.data_ptr(), tile_first.data_ptr(), n_tiles, out.data_ptr(), num_heads, num_kv_heads, head_dim,
-         int(window or 0), float(scale), error_flag(q.device).data_ptr(), ops._stream())
+         int(window or 0), float(scale), splits, None if part_o is None else part_o.data_ptr(),
+         None if part_ml is None else part_ml.data_ptr(), error_flag(q.device).data_ptr(), ops._stream())
 
 
 def decode(q, k_base, v_base, page_stride, page_size, block_table, row_list, n_rows, row_seg, positions, out, workspace, *,
@@ -167,10 +193,12 @@ def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, w
             raise KernelError(f"attention_flash: {name} must be bfloat16")
     if ctx.n_q_tiles and ctx.n_q_tiles_large and tc5_supports(head_dim, cache.page_size) and cache.num_pages \
             and ctx.extra.get("prefill_kernel") != "mma_sync":
+        longest = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n > 1)
+        splits = ctx.extra.get("prefill_splits") or tc5_splits(ctx.n_q_tiles_large, num_heads, longest, _sms(q.device), window)
         prefill_tc5(q, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
                     group.block_table, ctx.seg_start, ctx.seg_ctx_len, ctx.q_tile_large_seg, ctx.q_tile_large_first,
                     ctx.n_q_tiles_large, out, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-                    window=window, scale=scale)
+                    window=window, scale=scale, splits=splits, workspace=ctx.workspace)
     elif ctx.n_q_tiles:
         prefill(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.seg_start,
                 ctx.seg_ctx_len, ctx.q_tile_seg, ctx.q_tile_first, ctx.n_q_tiles, out, num_heads=num_heads,

@@ -336,7 +336,7 @@ def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
     return out
 
 
-def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True):
+def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True, tile_splits=1):
     from purhie_b200.csrc import flash
     from purhie_b200.parts.context import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -354,7 +354,7 @@ def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True
         flash.prefill_tc5(case["q"], case["T"], case["k_base"], case["v_base"], case["page_stride"], page_size,
                           case["pool"].shape[0], case["table"], case["seg_start"], case["seg_ctx"], i32([b[0] for b in big]),
                           i32([b[1] for b in big]), len(big), out, num_heads=HQ, num_kv_heads=HKV, head_dim=D,
-                          window=window, scale=scale)
+                          window=window, scale=scale, splits=tile_splits, workspace=Workspace(DEV))
         flash.check_errors(DEV)
     elif tile_seg:
         flash.prefill(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"],
@@ -410,6 +410,13 @@ def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
             o2 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp, bulk=bulk)
             assert not torch.isnan(o2.float()).any()
             assert rel(o2.cpu(), ref) < 1e-2
+    # several CTAs on the keys of one prompt tile, more than a short tile has blocks too
+    from purhie_b200.csrc import flash
+    if flash.tc5_supports(D, page_size):
+        for ts in (2, 5, 16):
+            o4 = run_flash(case, HQ, HKV, D, page_size, window, scale, tile_splits=ts)
+            assert not torch.isnan(o4.float()).any()
+            assert rel(o4.cpu(), ref) < 1e-2, ts
     # few CTAs: each walks many items, the stage ring and the query buffers wrap many times
     for sp, ctas in ((2, 3), (2, 1), (3, 1), (1, 2)):
         o3 = run_flash(case, HQ, HKV, D, page_size, window, scale, splits=sp, max_ctas=ctas)
