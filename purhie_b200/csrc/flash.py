@@ -193,7 +193,7 @@ def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, w
             raise KernelError(f"attention_flash: {name} must be bfloat16")
     if ctx.n_q_tiles and ctx.n_q_tiles_large and tc5_supports(head_dim, cache.page_size) and cache.num_pages \
             and ctx.extra.get("prefill_kernel") != "mma_sync":
-        longest = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n > 1)
+        longest = ctx.prefill_max_ctx or max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n > 1)
         splits = ctx.extra.get("prefill_splits") or tc5_splits(ctx.n_q_tiles_large, num_heads, longest, _sms(q.device), window)
         prefill_tc5(q, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
                     group.block_table, ctx.seg_start, ctx.seg_ctx_len, ctx.q_tile_large_seg, ctx.q_tile_large_first,

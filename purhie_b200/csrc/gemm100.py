@@ -7,6 +7,7 @@ float32 partial results are summed by the kernel that consumes the product.  Man
 """
 from __future__ import annotations
 
+import functools
 from ctypes import c_int, c_void_p
 from typing import Optional
 
@@ -36,10 +37,13 @@ def supports(weight: torch.Tensor) -> bool:
 
 
 def error_flag(device) -> torch.Tensor:
-    key = torch.device(device)
-    if key not in _flags:
-        _flags[key] = torch.zeros(1, dtype=torch.int32, device=key)
-    return _flags[key]
+    flag = _flags.get(device)
+    if flag is None:
+        key = torch.device(device)
+        if key not in _flags:
+            _flags[key] = torch.zeros(1, dtype=torch.int32, device=key)
+        flag = _flags[device] = _flags[key]
+    return flag
 
 
 def check_errors(device) -> None:
@@ -92,6 +96,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: in
     return out
 
 
+@functools.lru_cache(maxsize=4096)
 def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     """(swapped, block_n, splits) for a product of M tokens with an [N, K] weight.
 
@@ -117,6 +122,7 @@ def plan(M: int, N: int, K: int, sms: int, allow_split: bool):
     return True, block_n, splits
 
 
+@functools.lru_cache(maxsize=4096)
 def plan_many(M: int, N: int, K: int, sms: int, allow_split: bool, fused_epilogue: bool = False):
     """(pair, splits) for a product of M >= 128 tokens in the plain orientation: the one-CTA kernel (tiles of 128
     tokens x 256 features) or the pair kernel (256 x 256 on two SMs), and into how many parts K is cut.

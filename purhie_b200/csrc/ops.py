@@ -33,8 +33,28 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+_stream_now: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The stream the launchers use: the current one, looked up once per :func:`on_current_stream` scope."""
+    return _stream_now if _stream_now is not None else torch.cuda.current_stream().cuda_stream
+
+
+class on_current_stream:
+    """Inside this scope every launcher uses the stream that was current when the scope was entered, without asking
+    torch again for each of the few hundred launches of a step."""
+
+    def __enter__(self):
+        global _stream_now
+        self._before = _stream_now
+        _stream_now = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _stream_now
+        _stream_now = self._before
+        return False
 
 
 def _need(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:

@@ -70,6 +70,7 @@ class _Layout:
     n_tiles: int
     decode_max_ctx: int
     n_tiles_large: int = 0
+    prefill_max_ctx: int = 0
 
 
 @dataclass
@@ -80,6 +81,16 @@ class _DecodeGraph:
     logits: Optional[torch.Tensor] = None
     rows: Optional[torch.Tensor] = None
     launches: int = 0
+
+
+def _bucket(n: int) -> int:
+    """0, or the power of two (at least 256) that n fits."""
+    if n <= 0:
+        return 0
+    b = 256
+    while b < n:
+        b *= 2
+    return b
 
 
 class PendingTokens:
@@ -133,6 +144,10 @@ class Engine:
         self.max_graph_batch = max_graph_batch
         self.max_graphs = max_graphs
         self._graphs: Dict[tuple, _DecodeGraph] = {}
+        self.graph_prompts = True                       # batches with prompt portions are captured when they recur
+        self.max_prompt_graphs = 8
+        self._step_graphs: Dict[tuple, _DecodeGraph] = {}
+        self._step_seen: Dict[tuple, int] = {}
         self.last_upload_bytes = 0
         from ..csrc.build import load_library
         for lib in model.required_libraries():          # compile what this model needs, now
@@ -255,7 +270,7 @@ class Engine:
                 flat += cache.token_slots(e.request_id, g.index, cache.length(e.request_id), len(e.tokens))
         flat += (decode_rows or [0]) + (tile_seg or [0]) + (tile_first or [0]) + (big_seg or [0]) + (big_first or [0])
         return _Layout(flat, sizes, T, S, widths, q_lens, ctx_lens, len(want), len(decode_rows), len(tile_seg),
-                       decode_max_ctx, len(big_seg))
+                       decode_max_ctx, len(big_seg), max([c for c, n in zip(ctx_lens, q_lens) if n > 1], default=0))
 
     def _upload(self, flat: List[int], dev: torch.Tensor) -> None:
         """One copy of the metadata to the device, through two pinned buffers used in turn: a buffer is
@@ -286,7 +301,8 @@ class Engine:
                           seg_ctx_len=parts[4], seg_slot=parts[5], q_lens=lay.q_lens, ctx_lens=lay.ctx_lens,
                           groups=groups, workspace=workspace, compute_dtype=self.dtype, decode_only=lay.n_tiles == 0,
                           decode_rows=None if lay.n_tiles == 0 else parts[7 + 2 * G], n_decode_rows=lay.n_decode,
-                          decode_max_ctx=lay.decode_max_ctx, q_tile_seg=parts[8 + 2 * G],
+                          decode_max_ctx=_bucket(lay.decode_max_ctx), prefill_max_ctx=_bucket(lay.prefill_max_ctx),
+                          q_tile_seg=parts[8 + 2 * G],
                           q_tile_first=parts[9 + 2 * G], n_q_tiles=lay.n_tiles, q_tile_large_seg=parts[10 + 2 * G],
                           q_tile_large_first=parts[11 + 2 * G], n_q_tiles_large=lay.n_tiles_large)
         return ctx, parts[6]
@@ -318,15 +334,68 @@ class Engine:
         elif device_tokens is not None:
             raise StepError("token ids from the device need a batch of single tokens that runs as a graph")
         else:
-            ctx, want_rows, n_want = self.build_context(entries)
-            logits = self.model.forward(ctx, self.views, want_rows, n_want)
-            T, q_lens = ctx.T, ctx.q_lens
+            logits, T, q_lens, n_want = self._step_any(entries)
         for e in entries:
             self.cache.advance(e.request_id, len(e.tokens))
         self.last_stats = StepStats(tokens=T, prompt_rows=sum(q for q in q_lens if q > 1),
                                     decode_rows=sum(1 for q in q_lens if q == 1), wanted=n_want,
                                     pages_free=self.cache.free_pages())
         return logits
+
+    # ---- batches with prompt portions -----------------------------------------------------------------
+    def _step_any(self, entries: Sequence[StepEntry]):
+        """A batch with prompt portions.  Its launches depend on the lengths of the portions, the number of wanted
+        rows, the width of the block tables and (in powers of two) how far back the portions and the decode rows
+        look, not on the tokens: a combination that comes a second time (the chunks of a long prompt, a scheduler's
+        steady mix) is captured as a graph with scratch memory of its own and replayed from then on, which takes the
+        few hundred launcher calls of a step off the host.  Returns (logits, T, q_lens, wanted)."""
+        ps = self.page_size
+        need = max(-(-(self.cache.length(e.request_id) + len(e.tokens)) // ps) for e in entries) if self.cache.groups else 1
+        width = 8
+        while width < need:
+            width *= 2
+        lay = self._layout(entries, table_width=width)
+        key = (tuple(lay.q_lens), tuple(len(e.want) for e in entries), tuple(lay.widths), _bucket(lay.decode_max_ctx),
+               _bucket(lay.prefill_max_ctx))
+        g = self._step_graphs.get(key) if self.cuda_graphs and self.graph_prompts else None
+        if g is None and self.cuda_graphs and self.graph_prompts:
+            seen = self._step_seen.get(key, 0)
+            if len(self._step_seen) > 4096:
+                self._step_seen.clear()
+            self._step_seen[key] = seen + 1
+            if seen >= 1:
+                while len(self._step_graphs) >= self.max_prompt_graphs:
+                    self._step_graphs.pop(next(iter(self._step_graphs)))
+                g = _DecodeGraph(Workspace(self.device), torch.empty(len(lay.flat), dtype=torch.int32, device=self.device))
+                self._step_graphs[key] = g
+        if g is None:
+            dev = self.workspace.get("step_meta", (len(lay.flat),), torch.int32)
+            self._upload(lay.flat, dev)
+            ctx, want_rows = self._context(lay, dev, self.workspace)
+            return self._forward(ctx, want_rows, lay.n_want), lay.T, lay.q_lens, lay.n_want
+        self._step_graphs[key] = self._step_graphs.pop(key)               # most recently used last
+        self._upload(lay.flat, g.meta)
+        from ..csrc import ops
+        if g.graph is None:
+            ctx, want_rows = self._context(lay, g.meta, g.workspace)
+            g.logits = self._forward(ctx, want_rows, lay.n_want)           # this step's result, and every first-use set-up
+            g.workspace.frozen = True
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                self._forward(ctx, want_rows, lay.n_want)
+            g.launches = ops.launches - before
+            ops.launches = before
+            g.graph = graph
+        else:
+            g.graph.replay()
+            ops.launches += g.launches
+        return g.logits, lay.T, lay.q_lens, lay.n_want
+
+    def _forward(self, ctx, want_rows, n_want):
+        from ..csrc import ops
+        with ops.on_current_stream():
+            return self.model.forward(ctx, self.views, want_rows, n_want)
 
     # ---- decoding through CUDA graphs --------------------------------------------------------------
     def decodes_as_graph(self, entries: Sequence[StepEntry]) -> bool:
@@ -366,13 +435,13 @@ class Engine:
             ctx.decode_max_ctx = ctx_bucket      # the number of attention splits must not change between replays
             # the first time: run the launches directly (this is the step's result, and whatever a kernel
             # sets up on first use is set up), then capture the same launches for the next time
-            g.logits = self.model.forward(ctx, self.views, all_rows, S)
+            g.logits = self._forward(ctx, all_rows, S)
             g.workspace.frozen = True
             from ..csrc import ops
             graph = torch.cuda.CUDAGraph()
             before = ops.launches
             with torch.cuda.graph(graph):
-                self.model.forward(ctx, self.views, all_rows, S)
+                self._forward(ctx, all_rows, S)
             g.launches = ops.launches - before
             ops.launches = before
             g.graph = graph

@@ -90,7 +90,8 @@ class StepContext:
     # rows of single-token segments (None when every row is one: the list is then 0 .. T-1)
     decode_rows: Optional[torch.Tensor] = None
     n_decode_rows: int = 0
-    decode_max_ctx: int = 0
+    decode_max_ctx: int = 0              # how far back the decode rows look, as the power of two that holds it
+    prefill_max_ctx: int = 0             # the same for the prompt portions
     # the other segments cut into tiles of Q_TILE rows: segment and first row (within the portion) of each tile
     q_tile_seg: Optional[torch.Tensor] = None
     q_tile_first: Optional[torch.Tensor] = None
