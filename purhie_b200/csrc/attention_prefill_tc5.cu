@@ -237,10 +237,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
-    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // only now, with this CTA's tensor memory in hand: a kernel started early beside it must not take the columns
+    // this CTA still waits for while it waits for this kernel to end
+    pdl_launch_dependents();
     pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_o = tmem_base + 64;

@@ -719,13 +719,15 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    // The cluster kernel is launched in plain stream order, not as a programmatic dependent: started early, under a
+    // kernel that still ran, it was seen to stop the device now and then (a step of 512 prompt tokens beside eight
+    // decode rows, in two runs of three; never without the early start, never with the one-CTA kernel in its
+    // place).  It still lets the kernel behind it start early.
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, ma, mb, p) != cudaSuccess) {}
     return check_launch("gemm_tcgen05_pair");
 }

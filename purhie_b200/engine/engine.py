@@ -144,7 +144,8 @@ class Engine:
         self.max_graph_batch = max_graph_batch
         self.max_graphs = max_graphs
         self._graphs: Dict[tuple, _DecodeGraph] = {}
-        self.graph_prompts = True                       # batches with prompt portions are captured when they recur
+        self.graph_prompts = True                       # batches with prompt portions are captured when they recur ...
+        self.graph_prompt_tokens = 1024                 # ... and are small enough for the host's launches to be what they wait for
         self.max_prompt_graphs = 8
         self._step_graphs: Dict[tuple, _DecodeGraph] = {}
         self._step_seen: Dict[tuple, int] = {}
@@ -346,9 +347,10 @@ class Engine:
     def _step_any(self, entries: Sequence[StepEntry]):
         """A batch with prompt portions.  Its launches depend on the lengths of the portions, the number of wanted
         rows, the width of the block tables and (in powers of two) how far back the portions and the decode rows
-        look, not on the tokens: a combination that comes a second time (the chunks of a long prompt, a scheduler's
-        steady mix) is captured as a graph with scratch memory of its own and replayed from then on, which takes the
-        few hundred launcher calls of a step off the host.  Returns (logits, T, q_lens, wanted)."""
+        look, not on the tokens: a combination of at most graph_prompt_tokens tokens that comes a third time (the
+        chunks of a long prompt, a scheduler's steady mix) is captured as a graph with scratch memory of its own and
+        replayed from then on, which takes the few hundred launcher calls of a step off the host; larger batches keep
+        the device busy longer than the host needs to launch them.  Returns (logits, T, q_lens, wanted)."""
         ps = self.page_size
         need = max(-(-(self.cache.length(e.request_id) + len(e.tokens)) // ps) for e in entries) if self.cache.groups else 1
         width = 8
@@ -363,7 +365,7 @@ class Engine:
             if len(self._step_seen) > 4096:
                 self._step_seen.clear()
             self._step_seen[key] = seen + 1
-            if seen >= 1:
+            if seen >= 2 and lay.T <= self.graph_prompt_tokens:
                 while len(self._step_graphs) >= self.max_prompt_graphs:
                     self._step_graphs.pop(next(iter(self._step_graphs)))
                 g = _DecodeGraph(Workspace(self.device), torch.empty(len(lay.flat), dtype=torch.int32, device=self.device))

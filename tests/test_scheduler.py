@@ -178,3 +178,59 @@ def test_window_group_lets_a_long_request_live_in_few_pages():
     s.add(Request("w", [1, 2, 3], max_new_tokens=40))
     run_all(s, eng)
     assert s.finished["w"].stop_reason == STOP_MAX_TOKENS and len(s.finished["w"].output) == 40
+
+
+class AheadEngine(FakeEngine):
+    """A FakeEngine that also takes a step's token ids "from the device" (what the step before sampled, not yet
+    handed to the host) and samples without being waited for, as the scheduler's decode_ahead uses them."""
+
+    class Pending:
+        def __init__(self, toks):
+            self.ids = toks
+
+        def result(self):
+            return list(self.ids)
+
+    def decodes_as_graph(self, entries):
+        return all(len(e.tokens) == 1 for e in entries)
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            entries = [type(e)(e.request_id, [int(t)], e.want) for e, t in zip(entries, device_tokens)]
+        return super().step(entries)
+
+    def sample_async(self, logits, samplers):
+        return self.Pending(self.sample(logits, samplers))
+
+
+def run_to_the_end(sched, eng):
+    guard = 0
+    while sched.has_work():
+        if not sched.decode_ahead():
+            sched.step()
+        for r in list(sched.waiting):
+            eng.forget(r.request_id)
+        guard += 1
+        assert guard < 10000
+    return sched.finished
+
+
+def test_decoding_ahead_of_the_host_changes_no_output_and_ends():
+    """Budgets that end at different steps, an end-of-generation id on the way, pages that run out in the middle of a
+    run ahead: the same outputs and stop reasons as step by step, and the loop ends."""
+    prompts = {"a": list(range(1, 14)), "b": list(range(3, 12)), "c": list(range(2, 9)), "d": [4, 4]}
+    budgets = {"a": 12, "b": 5, "c": 9, "d": 30}
+    eos = [expected_output(prompts["d"], 30)[11]]
+    for pages in (64, 13):
+        outs = []
+        for ahead in (False, True):
+            eng = AheadEngine(num_pages=pages)
+            s = Scheduler(eng, max_batch_tokens=64, prefill_chunk=64)
+            s.run_ahead = ahead
+            for k, p in prompts.items():
+                s.add(Request(k, p, max_new_tokens=budgets[k], eos_ids=eos if k == "d" else ()))
+            run_to_the_end(s, eng)
+            outs.append({k: (s.finished[k].output, s.finished[k].stop_reason) for k in prompts})
+            assert eng.cache.free_pages() == [pages] and eng.cache.slots.num_free == 4
+        assert outs[0] == outs[1]
+        assert outs[0]["d"][1] == STOP_EOG and outs[0]["b"][1] == STOP_MAX_TOKENS
