@@ -383,7 +383,7 @@ class Model:
                 results[i] = self._emit(st, int(tok))
         return results
 
-    def _judge(self, st: Stream, tok: int, in_cache: int) -> str:
+    def _take_token(self, st: Stream, tok: int, in_cache: int) -> str:
         """Take the sampled token: "eog" (not emitted), "stop" (emitted, the stream ends) or "go".  ``in_cache``:
         tokens of the sequence before this one."""
         o = st.options
@@ -404,7 +404,7 @@ class Model:
         return "stop"
 
     def _emit(self, st: Stream, tok: int):
-        verdict = self._judge(st, tok, len(self._seqs[st.seq].tokens))
+        verdict = self._take_token(st, tok, len(self._seqs[st.seq].tokens))
         if verdict == "eog":
             return (False, None)
         if verdict == "go":
@@ -470,7 +470,7 @@ class Model:
             ended = []
             for j, ((i, st), s, tok) in enumerate(zip(live, seqs, toks)):
                 tok = int(tok)
-                verdict = self._judge(st, tok, len(s.tokens))
+                verdict = self._take_token(st, tok, len(s.tokens))
                 if fed_logits is None:                       # not fed yet: as in a step-by-step call
                     if verdict == "go":
                         st.next_token = tok

@@ -22,7 +22,9 @@ static inline __half __float2half(float f) { __half h; h.v = f; return h; }
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    ref = sys.argv[1]
     with tempfile.TemporaryDirectory() as tmp:
         os.makedirs(os.path.join(tmp, "hip"))
         with open(os.path.join(tmp, "hip", "hip_fp16.h"), "w") as f:
