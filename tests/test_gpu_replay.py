@@ -97,6 +97,39 @@ def test_first_tokens_and_long_decoding(tmp_path_factory):
         check(got, {"r6": ref["r6"]}, dtype, f"token by token/{dtype}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_recurring_batch_shape_is_replayed_as_a_graph_with_the_same_logits(dtype, tmp_path_factory):
+    """A prompt fed in equal chunks beside a decoding request: from the third chunk on the step is a captured graph
+    with scratch memory of its own.  The logits are those of an engine that launches every step kernel by kernel
+    (equal bits in float32), a new context bucket or table width makes a new graph, and both agree with the plain
+    implementation."""
+    from purhie_b200.engine import Engine, StepEntry
+    folder, reqs, ref, page = setup("B", dtype, tmp_path_factory)
+    long_req, other = reqs["r6"], reqs["r2"]                      # 250 and 97 tokens
+    chunk = 24
+
+    def run(graphs):
+        eng = Engine.from_folder(folder, dtype=dtype, page_size=page, max_tokens=512, max_requests=2)
+        eng.graph_prompts = graphs
+        eng.add_request("p"); eng.add_request("d")
+        eng.step([StepEntry("d", other[:60], [])])
+        rows_p, rows_d = [], []
+        for k, start in enumerate(range(0, 240, chunk)):
+            lg = eng.step([StepEntry("p", long_req[start:start + chunk], list(range(chunk))),
+                           StepEntry("d", other[60 + k:61 + k], [0])]).clone()
+            rows_p.append(lg[:chunk]); rows_d.append(lg[chunk:])
+        return torch.cat(rows_p), torch.cat(rows_d), eng
+
+    a_p, a_d, plain_eng = run(False)
+    b_p, b_d, graph_eng = run(True)
+    assert not plain_eng._step_graphs and len(graph_eng._step_graphs) >= 2      # the context bucket grew on the way
+    assert all(g.graph is not None for g in graph_eng._step_graphs.values())
+    if dtype == "float32":
+        assert torch.equal(a_p, b_p) and torch.equal(a_d, b_d)
+    check({"p": b_p, "d": b_d}, {"p": ref["r6"][:240], "d": ref["r2"][60:70]}, dtype, f"graph replay/{dtype}")
+    check({"p": a_p, "d": a_d}, {"p": ref["r6"][:240], "d": ref["r2"][60:70]}, dtype, f"launch by launch/{dtype}")
+
+
 def test_step_refuses_bad_batches_and_leaves_the_cache_alone(tmp_path_factory):
     from purhie_b200.cache import OutOfPages
     from purhie_b200.engine import Engine, StepEntry, StepError
