@@ -236,6 +236,18 @@ class CacheManager:
         """Physical token slots (page * page_size + offset) of positions ``[start, start + n)``."""
         table = self.requests[request_id].tables[group]
         ps = self.page_size
+        if n >= 64:
+            # a long portion: page by page instead of token by token
+            out = []
+            p = start
+            while p < start + n:
+                page = table[p // ps]
+                if page < 0:
+                    raise RuntimeError(f"request {request_id!r}: position {p} lies in a page that was given back")
+                stop = min(start + n, (p // ps + 1) * ps)
+                out.extend(range(page * ps + p % ps, page * ps + p % ps + (stop - p)))
+                p = stop
+            return out
         out = []
         for p in range(start, start + n):
             page = table[p // ps]

@@ -198,10 +198,14 @@ class Engine:
             n = len(e.tokens)
             if n < 1:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary of "
-                                    f"{self.vocab_size}")
+            if n > 16:
+                lo, hi = min(e.tokens), max(e.tokens)            # one pass in C instead of a check per token
+                bad = lo if not 0 <= int(lo) else hi if not int(hi) < self.vocab_size else None
+            else:
+                bad = next((t for t in e.tokens if not 0 <= int(t) < self.vocab_size), None)
+            if bad is not None:
+                raise StepError(f"request {e.request_id!r}: token id {bad} is outside the vocabulary of "
+                                f"{self.vocab_size}")
             if self.cache.length(e.request_id) + n > self.max_position:
                 raise StepError(f"request {e.request_id!r} would reach position "
                                 f"{self.cache.length(e.request_id) + n}, the model's limit is {self.max_position}")
@@ -227,7 +231,7 @@ class Engine:
             start = cache.length(e.request_id)
             n = len(e.tokens)
             base = len(tokens)
-            tokens.extend(int(t) for t in e.tokens)
+            tokens.extend(e.tokens if type(e.tokens) is list else (int(t) for t in e.tokens))
             positions.extend(range(start, start + n))
             row_seg.extend([s] * n)
             seg_start.append(base + n)

@@ -145,3 +145,20 @@ def test_random_orders_lose_no_page(seed):
 class _null:
     def __enter__(self): return self
     def __exit__(self, *a): return False
+
+
+def test_slots_of_a_long_portion_are_those_of_its_tokens_one_by_one():
+    """Long portions are mapped page by page; the result is what mapping every token alone gives, also across pages
+    that a window has passed (which must raise either way)."""
+    cm = CacheManager([CacheNeed.pages(1, 8, None), CacheNeed.pages(1, 8, 40)], 16, 64, 2)
+    cm.add_request("a")
+    cm.reserve("a", 300)
+    for g in (0, 1):
+        for start, n in ((0, 300), (5, 200), (17, 64), (100, 199), (299, 1)):
+            one_by_one = sum((cm.token_slots("a", g, p, 1) for p in range(start, start + n)), [])
+            assert cm.token_slots("a", g, start, n) == one_by_one
+    cm.advance("a", 300)
+    cm.reserve("a", 80)                                       # the window group has given back its first pages
+    assert cm.token_slots("a", 1, 300, 80) == sum((cm.token_slots("a", 1, p, 1) for p in range(300, 380)), [])
+    with pytest.raises(RuntimeError):
+        cm.token_slots("a", 1, 0, 100)
