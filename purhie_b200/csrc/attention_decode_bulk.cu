@@ -55,7 +55,7 @@ struct BulkParams {
 };
 
 struct Item {
-    int i, t, g, split, z, lo, lo_page, b_first, b_last;
+    int i, t, g, split, z, lo, lo_page, b_first, b_last, n_blocks;
 };
 
 // Blocks of 64 keys start at the page that holds the first visible key, so a block is a whole number of pages.
@@ -70,6 +70,7 @@ __device__ __forceinline__ Item make_item(const BulkParams& p, int w) {
     it.lo = p.window > 0 ? max(0, it.z - p.window + 1) : 0;
     it.lo_page = it.lo - it.lo % p.page_size;
     const int n_blocks = (it.z - it.lo_page) / BLOCK_KEYS + 1;
+    it.n_blocks = n_blocks;
     const int per = (n_blocks + p.splits - 1) / p.splits;
     it.b_first = it.split * per;
     it.b_last = min(n_blocks, it.b_first + per) - 1;
@@ -158,11 +159,11 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
             __syncwarp();
             // The first item's leading blocks hold keys and values of earlier steps (block tables and positions were
             // uploaded before the step began): they are requested while the kernel in front still runs.  The block
-            // with the token's own position, the last of the last split, is not among them.
+            // with the token's own position, the row's last (whichever split it falls to), is not among them.
             int b_start = 0;
             if (!waited) {
                 int n_pre = min(nb, STAGES);
-                if (it.split == p.splits - 1) n_pre = min(n_pre, nb - 1);
+                if (it.b_last == it.n_blocks - 1) n_pre = min(n_pre, nb - 1);
                 for (; b_start < n_pre; ++b_start) {
                     if (lane == 0) mb::arrive_expect_tx(&full[stage], 2 * TILE);      // the ring is still empty
                     __syncwarp();
@@ -363,7 +364,7 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
                 }
                 const int h = it.g * G + r;
                 if (p.splits == 1) {
-                    p.out[((size_t)it.t * p.HQ + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+                    p.out[((size_t)it.t * p.HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
                 } else {
                     const size_t slot = ((size_t)it.i * p.HQ + h) * p.splits + it.split;
                     p.part_o[slot * D + d] = acc;
@@ -393,7 +394,7 @@ __global__ void attention_combine_bulk_kernel(const float* __restrict__ part_o, 
             acc += c * part_o[(slot0 + s) * D + d];
             ll += c * part_ml[(slot0 + s) * 2 + 1];
         }
-        out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+        out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
     }
 }
 

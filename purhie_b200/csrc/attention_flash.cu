@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(
         }
         __syncthreads();
     }
-    const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+    const float inv0 = l[0] == 0.0f ? 0.0f : 1.0f / l[0], inv1 = l[1] == 0.0f ? 0.0f : 1.0f / l[1];
     const size_t width = (size_t)HQ * D;
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) {
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
         }
         const int h = g * G + r;
         if (splits == 1) {
-            out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+            out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
         } else {
             const size_t slot = ((size_t)blockIdx.x * HQ + h) * splits + split;
             part_o[slot * D + d] = acc;
@@ -247,7 +247,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
             acc += c * part_o[(slot0 + s) * D + d];
             ll += c * part_ml[(slot0 + s) * 2 + 1];
         }
-        out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll > 0.0f ? acc / ll : 0.0f);
+        out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
     }
 }
 

@@ -439,7 +439,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (ok && n_blocks > 0) ok = mb::wait(o_full, (n_blocks - 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX);
         if (ok && p.splits == 1) {
             tc_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const float inv = l == 0.0f ? 0.0f : 1.0f / l;        // a row with no visible key gives 0; NaN stays NaN
             __nv_bfloat16* dst = p.out + (size_t)(row0 + first + r) * p.HQ * D + (size_t)h * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -527,7 +527,7 @@ attention_prefill_tc5_combine_kernel(const float* __restrict__ part_o, const flo
         acc.x += c * o[s].x; acc.y += c * o[s].y; acc.z += c * o[s].z; acc.w += c * o[s].w;
         l += c * ls[s];
     }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    const float inv = l == 0.0f ? 0.0f : 1.0f / l;        // a row with no visible key gives 0; NaN stays NaN
     __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     uint2 v;
     v.x = *(uint32_t*)&h0; v.y = *(uint32_t*)&h1;

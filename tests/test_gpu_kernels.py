@@ -591,3 +591,70 @@ def test_sample_chain_equals_the_host_chain(V):
         ops.sample_chain(dev, torch.from_numpy(rec.view(np.uint8).reshape(R, 24)).to(DEV), out)
         device = out.cpu().tolist()
         assert device == host, [(i, cases[i], host[i], device[i]) for i in range(R) if host[i] != device[i]]
+
+
+@pytest.mark.parametrize("ctx,splits", [(130, 4), (130, 1), (200, 3), (64, 2)])
+def test_decode_attention_sees_the_key_written_by_the_kernel_in_front(ctx, splits):
+    """The decode kernel starts under the kernel that writes the token's own key and value and requests older
+    blocks before it waits for that kernel; the block with the token's own position must wait, also when it is not
+    in the last split (130 tokens = 3 blocks in 4 splits: the last split is empty).  As in a model's step the three
+    kernels (a product, the writer, the attention) are replayed as a graph, with no host between them; the writer
+    works through 2,048 rows first to last while the attention takes them last first, and the slot is NaN until it
+    is written, so a request issued too early finds NaN (seen in a handful of rows per run with the check on the
+    split instead of on the block)."""
+    from purhie_b200.csrc import flash, ops
+    from purhie_b200.parts.context import Workspace
+    HQ, HKV, D, ps, R = 32, 8, 128, 16, 2048
+    scale = 1.0 / math.sqrt(D)
+    pages_per = -(-ctx // ps)
+    n_pages = R * pages_per + 1
+    g = torch.Generator(device=DEV).manual_seed(ctx)
+    pool = torch.randn(n_pages, 1, 2, HKV, ps, D, device=DEV, generator=g).bfloat16()
+    table = (torch.randperm(n_pages - 1, device=DEV, generator=g).int() + 1).view(R, pages_per).contiguous()
+    z = ctx - 1
+    own_page = table[:, z // ps].long()
+    slots = (own_page * ps + z % ps).int()
+    qkv = torch.randn(2, R, (HQ + 2 * HKV) * D, device=DEV, generator=g)         # two partial sums, as after a split product
+    q = torch.empty(R, HQ, D, dtype=torch.bfloat16, device=DEV)
+    out = torch.full((R, HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    pos = torch.full((R,), z, dtype=torch.int32, device=DEV)
+    row_seg = torch.arange(R, dtype=torch.int32, device=DEV)
+    last_first = torch.arange(R - 1, -1, -1, dtype=torch.int32, device=DEV)
+    ws = Workspace(DEV)
+    from purhie_b200.csrc import gemm100
+    gx, gw = rnd(8, 8192, dtype=torch.bfloat16, seed=1), rnd(16384, 8192, dtype=torch.bfloat16, seed=2)
+    gout = torch.empty(8, 16384, device=DEV)
+
+    def chain():
+        gemm100.gemm(gx, gw, gout, swapped=True, block_n=16, max_ctas=74)
+        ops.qk_norm_rope_kv_write(qkv, q, pos, num_heads=HQ, num_kv_heads=HKV, head_dim=D, eps=1e-6, q_norm=None, k_norm=None,
+                                  bias=None, cos_sin=None, n_rot=0, slot_mapping=slots, k_base=pool[0, 0, 0],
+                                  v_base=pool[0, 0, 1], page_stride=pool.stride(0), page_size=ps, splits=2, interleaved=False)
+        flash.decode_bulk(q, pool[0, 0, 0], pool[0, 0, 1], pool.stride(0), ps, n_pages, table, last_first, R, row_seg, pos, out, ws,
+                          num_heads=HQ, num_kv_heads=HKV, head_dim=D, window=None, scale=scale, splits=splits)
+
+    chain()                                                  # first use of every kernel, outside the capture
+    flash.check_errors(DEV)
+    ws.frozen = True
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), ops.on_current_stream():
+        chain()
+    for _ in range(3):
+        pool.view(-1, 2, HKV, ps, D)[own_page, :, :, z % ps] = float("nan")        # not written yet
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()                                       # as a step does: no host between the launches
+        flash.check_errors(DEV)
+        assert not torch.isnan(out.float()).any()
+    # and it is the right answer for a row
+    r = R - 3
+    gemm100.check_errors(DEV)
+    idx = table[r].long()
+    K = pool[idx, 0, 0].permute(0, 2, 1, 3).reshape(-1, HKV, D)[:ctx].double()
+    V = pool[idx, 0, 1].permute(0, 2, 1, 3).reshape(-1, HKV, D)[:ctx].double()
+    ref = []
+    for h in range(HQ):
+        kv = h // (HQ // HKV)
+        p = torch.softmax((K[:, kv] @ q[r, h].double()) * scale, 0)
+        ref.append(p @ V[:, kv])
+    assert rel(out[r].double(), torch.cat(ref)) < 5e-3
