@@ -26,7 +26,7 @@ def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt():
     from purhie_b200.engine import Engine, StepEntry
     cfg = Qwen3Config.from_dict(SHAPE)
     g = torch.Generator().manual_seed(11)
-    toks = torch.randint(0, cfg.vocab_size, (2600,), generator=g).tolist()
+    toks = torch.randint(0, cfg.vocab_size, (2700,), generator=g).tolist()
     others = [torch.randint(0, cfg.vocab_size, (n + 24,), generator=g).tolist() for n in (17, 300, 1000, 2047, 64, 129, 700)]
     out = {}
     for dtype in ("float32", "bfloat16"):
@@ -51,6 +51,8 @@ def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt():
         res["batch"] = torch.cat(rows)
         for i in range(len(others)):
             eng.release(i)
+        # a short portion late in the context: one attention tile that looks back over 2,600 keys, shared by several CTAs
+        res["late"] = eng.step([StepEntry("d", toks[2548:2600], [0, 25, 51])]).clone()
         eng.add_request("c")
         for s in range(0, 2500, 500):
             lg = eng.step([StepEntry("c", toks[s:s + 500], [499] if s + 500 >= 2500 else [])])
@@ -66,7 +68,9 @@ def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt():
     for name, want in (("decode", f32["whole"][1:]), ("chunks", f32["whole"][:1])):
         err = rel(b16[name], want)
         assert err < 1.5 * whole + 2e-3, f"{name}: {err:.3e} against {whole:.3e} for a whole prompt"
-    # the batch continues the same request for 24 more tokens: compare with the float32 engine's batch
-    err = rel(b16["batch"], f32["batch"])
-    assert err < 1.5 * whole + 2e-3, f"batch: {err:.3e} against {whole:.3e}"
-    assert not torch.isnan(b16["batch"]).any()
+    # the batch continues the same request for 24 more tokens, the late portion for 52 more: compare with the float32
+    # engine's own
+    for name in ("batch", "late"):
+        err = rel(b16[name], f32[name])
+        assert err < 1.5 * whole + 2e-3, f"{name}: {err:.3e} against {whole:.3e}"
+        assert not torch.isnan(b16[name]).any()
