@@ -18,9 +18,9 @@ from .ops import KernelError, call, register_signatures
 
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_void_p, c_void_p],
+                             c_int, c_int, c_void_p, c_void_p],
     "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p, c_void_p],
+                                  c_int, c_void_p, c_void_p],
 })
 
 BLOCK_K = 64
@@ -64,9 +64,10 @@ def sm_count(device) -> int:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, block_n: int, splits: int = 1,
-         max_ctas: int = 0, swiglu: bool = False) -> torch.Tensor:
+         max_ctas: int = 0, swiglu: bool = False, accumulate: bool = False) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1).  With
-    ``swiglu`` the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up."""
+    ``swiglu`` the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up.  ``accumulate``
+    (plain orientation, float32, one split): out += the product."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"gemm_tcgen05: {name} must be a contiguous bfloat16 CUDA tensor")
@@ -75,13 +76,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
     if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, error_flag(x.device).data_ptr(),
-         ops._stream())
+         1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, 1 if accumulate else 0,
+         error_flag(x.device).data_ptr(), ops._stream())
     return out
 
 
 def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: int = 1, max_clusters: int = 0,
-              swiglu: bool = False) -> torch.Tensor:
+              swiglu: bool = False, accumulate: bool = False) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T on pairs of CTAs (cta_group::2), tiles of 256 x 256; float32 partial sums
     [splits, M, N] when splits > 1; ``swiglu`` as in gemm."""
     for name, t in (("x", x), ("w", w)):
@@ -92,7 +93,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, splits: in
     if x.shape[-1] != K or out.numel() != splits * M * (N // 2 if swiglu else N) or not out.is_contiguous():
         raise KernelError(f"gemm_tcgen05_pair: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05_pair", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
-         splits, max_clusters, 1 if swiglu else 0, error_flag(x.device).data_ptr(), ops._stream())
+         splits, max_clusters, 1 if swiglu else 0, 1 if accumulate else 0, error_flag(x.device).data_ptr(), ops._stream())
     return out
 
 
@@ -152,7 +153,7 @@ def plan_many(M: int, N: int, K: int, sms: int, allow_split: bool, fused_epilogu
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, M: int, allow_split: bool,
-           fuse_swiglu: bool = False):
+           fuse_swiglu: bool = False, add_into: Optional[torch.Tensor] = None):
     """The product through the tcgen05 kernel.  ``fuse_swiglu`` (w holds (gate, up) row pairs): when the plain
     orientation runs, the activation is applied in the epilogue and the result [M, N / 2] is marked activated."""
     from ..parts.base import Addend
@@ -176,6 +177,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, ctx, out_name: str, out_dtype: torc
         out = ctx.workspace.get(out_name + "_act", (M, N // 2), out_dtype)
         gemm(x[:M], w, out, swapped=swapped, block_n=block_n, swiglu=True)
         return Addend(out, 1, activated=True)
+    if (add_into is not None and not swapped and splits == 1 and add_into.dtype == torch.float32 and add_into.is_contiguous()
+            and add_into.shape[-1] == N and add_into.numel() >= M * N):
+        # many tokens, K whole: the residual sum happens in the epilogue and the product never goes to memory
+        target = add_into.view(-1, N)[:M]
+        if pair:
+            gemm_pair(x[:M], w, target, accumulate=True)
+        else:
+            gemm(x[:M], w, target, swapped=False, block_n=block_n, accumulate=True)
+        return Addend(None, 0)
     if splits > 1:
         out = ctx.workspace.get(out_name + "_partial", (splits, M, N), torch.float32)
     else:

@@ -48,6 +48,7 @@ struct GemmParams {
     void* out;
     int out_bf16;        // 1: bfloat16 output, 0: float32
     int swapped;
+    int accumulate;      // 1: out (float32, plain orientation, one split) += the product: the residual sum in the epilogue
     int swiglu;          // 1: columns are (gate, up) pairs; out[a, j] = silu(D[a, 2j]) * D[a, 2j + 1] (plain orientation)
     long long ld;        // row length of out
     long long split_stride;
@@ -233,13 +234,23 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t*
         } else {
             float* o = (float*)p.out + base;
             if (full_chunk && ((uintptr_t)o & 15) == 0) {
+                if (p.accumulate) {
+                    float4 old[CH / 4];
 #pragma unroll
-                for (int j = 0; j < CH; j += 4)
-                    *(uint4*)(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    for (int j = 0; j < CH; j += 4) old[j / 4] = *(const float4*)(o + j);
+#pragma unroll
+                    for (int j = 0; j < CH; j += 4)
+                        *(float4*)(o + j) = make_float4(old[j / 4].x + __uint_as_float(r[j]), old[j / 4].y + __uint_as_float(r[j + 1]),
+                                                        old[j / 4].z + __uint_as_float(r[j + 2]), old[j / 4].w + __uint_as_float(r[j + 3]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CH; j += 4)
+                        *(uint4*)(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < CH; ++j)
-                    if (b0 + c + j < p.rows_b) o[j] = __uint_as_float(r[j]);
+                    if (b0 + c + j < p.rows_b) o[j] = p.accumulate ? o[j] + __uint_as_float(r[j]) : __uint_as_float(r[j]);
             }
         }
     } else {
@@ -738,8 +749,10 @@ PH_DEFINE_LAST_ERROR(ph_gemm100)
 
 // The same product on pairs of CTAs (tcgen05 cta_group::2): tiles of 256 tokens x 256 features, plain orientation;
 // float32 partial results [splits][M, N] with splits > 1.  max_clusters: 0 or a cap on the number of CTA pairs.
+// accumulate: out (float32, one split, no activation) += the product.
 PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                        int splits, int max_clusters, int swiglu, int* error_flag, cudaStream_t stream) {
+                                        int splits, int max_clusters, int swiglu, int accumulate, int* error_flag,
+                                        cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05_pair: bad arguments (M %d, N %d, K %d)", M, N, K);
     if (K % 8) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05_pair: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
@@ -748,13 +761,15 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     if (splits < 1 || splits > kblocks) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: %d splits for %d blocks of K", splits, kblocks);
     if (splits > 1 && out_dtype != PH_F32) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: partial results are float32");
     if (swiglu && ((N & 1) || splits > 1)) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue needs an even N and one split");
+    if (accumulate && (swiglu || splits > 1 || out_dtype != PH_F32))
+        return fail(PH_ERR_ARG, "gemm_tcgen05_pair: adding into the output needs float32, one split and no activation");
     CUtensorMap ma, mb;
     if (!make_map(&ma, x, M, K, BM) || !make_map(&mb, w, N, K, PAIR_HALF))
         return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cuTensorMapEncodeTiled failed (rows %d / %d, K %d)", M, N, K);
     GemmParams p;
     p.rows_a = M; p.rows_b = N; p.K = K;
     p.a_tiles = 0; p.b_tiles = 0; p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     return launch_pair(ma, mb, p, max_clusters, stream);
 }
@@ -763,9 +778,10 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
 // side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).
 // swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue
 // (the formula of src/gpu_ops.hip:103-114 in the reference).
+// accumulate: out (float32, plain orientation, one split, no activation) += the product.
 PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                   int swapped, int block_n, int splits, int max_ctas, int swiglu, int* error_flag,
-                                   cudaStream_t stream) {
+                                   int swapped, int block_n, int splits, int max_ctas, int swiglu, int accumulate,
+                                   int* error_flag, cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05: bad arguments (M %d, N %d, K %d)", M, N, K);
     if (K % 8) return fail(PH_ERR_UNSUPPORTED, "gemm_tcgen05: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
@@ -776,6 +792,8 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     if (swiglu && (splits > 1 || (N & 1) || (!swapped && block_n < 32)))
         return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs one split, an even N and, in the plain orientation, "
                                 "tiles of 32 features or more");
+    if (accumulate && (swapped || swiglu || splits > 1 || out_dtype != PH_F32))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: adding into the output needs the plain orientation, float32, one split and no activation");
     const void* a = swapped ? w : x;
     const void* b = swapped ? x : w;
     const int rows_a = swapped ? N : M, rows_b = swapped ? M : N;
@@ -786,7 +804,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
     p.a_tiles = (rows_a + BM - 1) / BM; p.b_tiles = (rows_b + block_n - 1) / block_n;
     p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     switch (block_n) {
         case 16: return launch<16>(ma, mb, p, max_ctas, stream);

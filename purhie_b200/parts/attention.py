@@ -137,7 +137,7 @@ class Attention(Mixer):
                                   ctx.row_seg, ctx.positions, out, num_heads=self.num_heads,
                                   num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
                                   scale=self.scale)
-        return self.o_proj(out, ctx, "o_out", torch.float32, rows=T, allow_split=True)
+        return self.o_proj(out, ctx, "o_out", torch.float32, rows=T, allow_split=True, add_into=ctx.residual)
 
 
 register_part("mixer", "attention", Attention)

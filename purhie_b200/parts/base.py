@@ -11,6 +11,7 @@ is handed them on the device by ``bind`` and then runs inside a step.  Four kind
 ``Mixer``             ``cache_need() -> CacheNeed`` tells the cache manager what to keep for it;
                       ``forward(x, ctx, cache) -> Addend`` mixes the tokens of each request.
 ``FeedForward``       ``forward(x, ctx) -> Addend`` maps [T, E] to [T, E] row by row.
+                      (Either may instead add its result into ``ctx.residual`` and return ``Addend(None)``.)
 
 plus the block arrangement that strings them together.  New parts are added with the ``register_*``
 functions; the generic decoder looks kinds up at build time, so a model description may name a part that
@@ -29,9 +30,10 @@ from ..weights.loader import TensorSpec
 
 @dataclass
 class Addend:
-    """A tensor to be added to the residual stream: [T, E], or [splits, T, E] partial sums."""
+    """A tensor to be added to the residual stream: [T, E], or [splits, T, E] partial sums; None when the part has
+    already added its result into ``ctx.residual``."""
 
-    tensor: torch.Tensor
+    tensor: Optional[torch.Tensor]
     splits: int = 1
     activated: bool = False      # a product whose activation was already applied in the kernel's epilogue
 

@@ -29,6 +29,7 @@ class PreNormBlock:
         return out
 
     def forward(self, stream, ctx, cache) -> None:
+        ctx.residual = stream.x
         xn = self.mixer_norm.forward(stream, ctx)
         stream.add(self.mixer.forward(xn, ctx, cache))
         xn = self.feed_forward_norm.forward(stream, ctx)

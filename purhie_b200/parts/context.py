@@ -92,6 +92,9 @@ class StepContext:
     n_decode_rows: int = 0
     decode_max_ctx: int = 0              # how far back the decode rows look, as the power of two that holds it
     prefill_max_ctx: int = 0             # the same for the prompt portions
+    # The float32 residual [T, E] that the addend a mixer or feed-forward returns will be added to.  A part may add
+    # its result into it itself (in the epilogue of its last product, say) and return Addend(None).
+    residual: Optional[torch.Tensor] = None
     # the other segments cut into tiles of Q_TILE rows: segment and first row (within the portion) of each tile
     q_tile_seg: Optional[torch.Tensor] = None
     q_tile_first: Optional[torch.Tensor] = None
@@ -122,4 +125,4 @@ class ResidualStream:
     def add(self, addend: Addend) -> None:
         if self.pending is not None:
             raise RuntimeError("the residual stream already has a pending addend")
-        self.pending = addend
+        self.pending = None if addend.tensor is None else addend          # None: the part added into x itself

@@ -55,7 +55,7 @@ class SwiGLU(FeedForward):
         else:
             act = ctx.workspace.get("ff_act", (T, self.intermediate_size), dt)
             ops.swiglu(gu.tensor, act, splits=gu.splits)
-        return self.down_proj(act, ctx, "ff_out", torch.float32, rows=T, allow_split=True)
+        return self.down_proj(act, ctx, "ff_out", torch.float32, rows=T, allow_split=True, add_into=ctx.residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -41,7 +41,10 @@ class Linear:
         return ("core", "gemm100") if self._fast_kernel() else ("core",)
 
     def __call__(self, x: torch.Tensor, ctx, out_name: str, out_dtype: torch.dtype, rows: Optional[int] = None,
-                 allow_split: bool = False, fuse_swiglu: bool = False) -> Addend:
+                 allow_split: bool = False, fuse_swiglu: bool = False, add_into: Optional[torch.Tensor] = None) -> Addend:
+        """x [rows, in] -> Addend of [rows, out].  ``add_into`` (float32 [rows, out]): where the kernel can add the
+        product in its epilogue it does, and the addend comes back empty; otherwise the product is returned as
+        usual and the caller's norm adds it."""
         M = rows if rows is not None else x.shape[0]
         ws = ctx.workspace
         if self.weight.dtype == torch.float32 and x.dtype != torch.float32:
@@ -50,7 +53,7 @@ class Linear:
             x = x32
         fast = self._fast_kernel()
         if fast and x.dtype == torch.bfloat16:
-            return fast.linear(x, self.weight, ctx, out_name, out_dtype, M, allow_split, fuse_swiglu)
+            return fast.linear(x, self.weight, ctx, out_name, out_dtype, M, allow_split, fuse_swiglu, add_into)
         out = ws.get(out_name, (M, self.out_features), out_dtype)
         ops.gemm_simple(x[:M], self.weight, out)
         return Addend(out, 1)

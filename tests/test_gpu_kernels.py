@@ -170,6 +170,25 @@ def test_gemm_tcgen05_swiglu_epilogue_with_few_tokens(M, N, K, block_n, out_dtyp
     assert rel(out, g / (1 + torch.exp(-g)) * u) < (3e-5 if out_dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 520, 200), (2048, 1024, 512)])
+def test_gemm_tcgen05_adds_into_the_output(M, N, K):
+    """The residual sum in the epilogue: out += x w^T, on one CTA per tile and on pairs, with the bits of a product
+    written out and added afterwards."""
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=27), rnd(N, K, dtype=torch.bfloat16, seed=28, scale=0.2)
+    base = rnd(M, N, seed=29)
+    prod = torch.empty(M, N, device=DEV)
+    gemm100.gemm(x, w, prod, swapped=False, block_n=256)
+    for pair in (False, True):
+        out = base.clone()
+        if pair:
+            gemm100.gemm_pair(x, w, out, accumulate=True)
+        else:
+            gemm100.gemm(x, w, out, swapped=False, block_n=256, accumulate=True)
+        gemm100.check_errors(DEV)
+        assert torch.equal(out, base + prod)
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     from purhie_b200.csrc import gemm100
     from purhie_b200.csrc.ops import KernelError
