@@ -79,10 +79,12 @@ template <> struct Vec4<__nv_bfloat16> {
     }
 };
 
-// Partial sums of a split product fetched at once (a decode step's o and down products come in nine parts).
-constexpr int PARTS_IN_FLIGHT = 12;
+// Partial sums of a split product fetched at once (a decode step's o and down products come in nine parts).  A
+// launch with one addend or none takes the kernel made for one: it needs half the registers, and with thousands of
+// rows it is the number of resident rows per SM that keeps the memory busy.
+constexpr int MANY_PARTS_IN_FLIGHT = 12;
 
-template <typename TA, typename TY, int MAX_IT>
+template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
                                        const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
@@ -232,8 +234,15 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
         if (n_out >= 1024 && E <= 4096 && threads > 256) threads = 256;
         const int iters = (E / 4 + threads - 1) / threads;
 #define LAUNCH_VEC(TA, TY, IT)                                                                                          \
-        launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT>, dim3(n_out), dim3(threads), 0, stream, x, (const TA*)add,   \
-                          add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x)
+        do {                                                                                                            \
+            if (!add || add_splits == 1)                                                                                \
+                launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, 1>, dim3(n_out), dim3(threads), 0, stream, x,      \
+                                  (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x); \
+            else                                                                                                        \
+                launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, MANY_PARTS_IN_FLIGHT>, dim3(n_out), dim3(threads), \
+                                  0, stream, x, (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E,     \
+                                  (TY*)y, write_x);                                                                     \
+        } while (0)
         PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, {
             if (iters == 1) LAUNCH_VEC(TA, TY, 1); else if (iters == 2) LAUNCH_VEC(TA, TY, 2); else LAUNCH_VEC(TA, TY, 4);
         }));
