@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on
 the device over exactly K decode steps after W warm-up steps; ``e2e`` is the same through the Python entry
@@ -24,7 +24,14 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, intermediate_size=12288,
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
                 max_position_embeddings=4096, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
-CONTEXT, PREFIX, PREFILL_TOKENS, SEED = 4096, 2048, 2048, 2
+# the other two benchmark shapes of BASELINE.json (configs[3] and configs[4]); the default run stays the 8B shape
+QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, intermediate_size=3072, num_attention_heads=16,
+                 num_key_value_heads=8, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
+                 num_key_value_heads=8)
+SHAPES = {"8b": ("Qwen3-8B", QWEN3_8B, 2, (1, 64)), "0.6b": ("Qwen3-0.6B", QWEN3_06B, 3, (1, 64)),
+          "32b": ("Qwen3-32B", QWEN3_32B, 4, (1, 32))}
+CONTEXT, PREFIX, PREFILL_TOKENS = 4096, 2048, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -95,8 +102,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
-                    help="fewer layers than the configuration's 36 (named in config); layer sizes stay")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the headline 8B shape or another")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (named in config); layer sizes stay")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
@@ -117,11 +125,14 @@ def main():
     from purhie_b200.engine import StepEntry
     from purhie_b200.sampling import SamplerParams
 
-    cfg = Qwen3Config.from_dict(dict(QWEN3_8B, num_hidden_layers=args.layers))
+    shape_name, shape, SEED, point_batches = SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = shape["num_hidden_layers"]
+    cfg = Qwen3Config.from_dict(dict(shape, num_hidden_layers=args.layers))
     pk = peaks()
     dev = "cuda:0"
     model = load_model_random(cfg, SEED, "bfloat16", dev)
-    max_batch = args.batch if args.phase != "all" else max(64, args.batch)
+    max_batch = args.batch if args.phase != "all" else max(max(point_batches), args.batch)
     if args.phase != "all":
         args.no_points = True
     model.kv_cache_init(CONTEXT, max_sequences=max_batch + 1, page_size=16,
@@ -173,7 +184,7 @@ def main():
         eng.step([StepEntry(i, ids(PREFIX), [])])
     torch.cuda.synchronize()
 
-    weight_bytes = 2.0 * (cfg.num_hidden_layers * layer_mm + V * E)
+    weight_bytes = 2.0 * (cfg.num_hidden_layers * layer_mm + V * E)       # the embedding table is gathered, not streamed
     kv_bytes_per_token = 2.0 * 2 * cfg.num_hidden_layers * kvw
 
     def decode_run(batch, steps, warmup):
@@ -206,7 +217,7 @@ def main():
     clocks = sampler.stop()
     points = {}
     if not args.no_points:
-        for b in (1, 64):
+        for b in point_batches:
             ms_b, _, by = decode_run(b, min(args.steps, 32), 3)
             points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
             points[f"decode_b{b}_hbm_frac"] = round(by / (ms_b * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
@@ -242,15 +253,15 @@ def main():
     value = args.batch / ms_step * 1e3
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 from 2,048-token prefixes (Qwen3-8B shape)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch {args.batch} from 2,048-token prefixes ({shape_name} shape)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B shape, random weights seed 2", "global_batch": args.batch, "seq_len": PREFIX,
+        "config": {"model": f"{shape_name} shape, random weights seed {SEED}", "global_batch": args.batch, "seq_len": PREFIX,
                    "context": CONTEXT, "parallelism": "single GPU", "layers": args.layers,
-                   "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": E, "q_heads": cfg.num_attention_heads,
+                   "layers_of_config": shape["num_hidden_layers"], "hidden": E, "q_heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": D, "intermediate": FF, "vocab": V,
-                   "kv_page_tokens": 16, "kv_dtype": "bf16", "l2": "weights (>=16 GB) exceed L2 every step",
+                   "kv_page_tokens": 16, "kv_dtype": "bf16", "l2": f"weights ({weight_bytes / 1e9:.1f} GB) exceed L2 every step",
                    "cuda_graphs": True, "prefill_tokens": PREFILL_TOKENS},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
