@@ -467,7 +467,6 @@ class Engine:
         """Start sampling one token per row on the device and their copy to the host without waiting for either.
         Returns None when the rows' samplers do not all run the same device kernel (see :meth:`sample`).  Each
         sampler draws its uniform number now."""
-        import numpy as np
         from ..csrc import ops
         R = len(samplers)
         if logits is None or logits.shape[0] != R:

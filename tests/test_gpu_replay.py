@@ -152,3 +152,48 @@ def test_step_refuses_bad_batches_and_leaves_the_cache_alone(tmp_path_factory):
         eng.step([StepEntry("b", list(range(10)), []), StepEntry("a", list(range(30)), [])])
     assert eng.cache.free_pages() == free and eng.length("a") == 40 and eng.length("b") == 0
     eng.cache.check()
+
+
+@pytest.mark.parametrize("seed", [3, 5, 8, 13, 21, 35])
+def test_drawn_configurations_and_schedules(seed, tmp_path):
+    """Configurations drawn at random (head sizes 16 to 128 in steps of 16, one to four groups of one to eight heads,
+    widths and vocabularies that are no power of two, windows on some layers, pages of 8 to 32 tokens) under drawn
+    schedules, in both precisions.  In float32 a different argmax is accepted only where the plain implementation's
+    two best logits are within 1e-5 of the largest."""
+    import random
+    from purhie_b200.engine import Engine
+    rng = random.Random(seed)
+    D = rng.choice([16, 32, 64, 64, 128, 128, 48, 80])
+    HKV = rng.choice([1, 2, 3, 4])
+    L = rng.randint(1, 3)
+    cfg_dict = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=L, hidden_size=8 * rng.randint(4, 40),
+                    intermediate_size=8 * rng.randint(6, 80), num_attention_heads=HKV * rng.choice([1, 2, 3, 4, 5, 8]),
+                    num_key_value_heads=HKV, head_dim=D, vocab_size=rng.randint(100, 3000), max_position_embeddings=512,
+                    rope_theta=rng.choice([1e4, 1e6]), rms_norm_eps=rng.choice([1e-6, 1e-5]),
+                    tie_word_embeddings=rng.random() < 0.5, attention_bias=rng.random() < 0.3)
+    if rng.random() < 0.5:
+        cfg_dict.update(layer_types=[rng.choice(["full_attention", "sliding_attention"]) for _ in range(L)],
+                        sliding_window=rng.choice([8, 24, 40, 100, 200]))
+    init = dict(seed=seed, std=rng.choice([0.02, 0.05]), scale_low=0.8, scale_high=1.2, page_size=rng.choice([8, 16, 32]))
+    lengths = [rng.choice([1, 2, 3, 17, 33, 64, 65, 127, 128, 129, 200, 255, 256, 257, 300, 400, 511])
+               for _ in range(rng.randint(3, 5))]
+    sizes = [rng.choice([1, 2, 3, 5, 8, 13, 16, 17, 31, 64, 100, 130]) for _ in range(11)]
+    for dtype in ("float32", "bfloat16"):
+        folder = tmp_path / dtype
+        cfg = make_model(folder, cfg_dict, init, dtype)
+        reqs = {f"r{i}": random_tokens(n, cfg.vocab_size, 1000 * seed + i) for i, n in enumerate(lengths)}
+        pc, pw = P.read_model(str(folder))
+        ref = {rid: P.forward(pc, pw, toks) for rid, toks in reqs.items()}
+        for mode, steps, max_tokens in (("tail32", schedule_tail(reqs), 512),
+                                        ("portions", schedule_portions(reqs, sizes=sizes), 512),
+                                        ("mixed", schedule_mixed(reqs, seed=seed), 4 * (-(-max(lengths) // 64) * 64))):
+            eng = Engine.from_folder(str(folder), dtype=dtype, page_size=init["page_size"], max_tokens=max_tokens,
+                                     max_requests=4, poison_cache=True)
+            step, release = engine_runner(eng)
+            got = run_schedule(step, release, steps)
+            for rid in ref:
+                what = f"seed {seed} {cfg_dict} {dtype}/{mode}/{rid}"
+                assert rel_err(got[rid], ref[rid]) < TOL[dtype], what
+                gap = 1e-5 if dtype == "float32" else 0.1
+                assert not same_top1_or_near_tie(got[rid], ref[rid], gap=gap), what
+            eng.cache.check()
