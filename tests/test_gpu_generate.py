@@ -192,6 +192,30 @@ def test_scheduler_running_ahead_changes_no_token(models):
         assert steps_b <= steps_a + 2                        # at most the step in flight when a request ended is extra
 
 
+def test_pages_run_out_on_the_device_and_every_request_still_gets_its_tokens(models):
+    """Five greedy requests in a pool that holds about two of them: the scheduler preempts the newest, which starts
+    over later on pages that others have used meanwhile, and every output is what the request gives alone."""
+    from purhie_b200.api import load_model
+    from purhie_b200.engine.scheduler import Request, Scheduler
+    from purhie_b200.sampling import SamplerParams
+    folder, cfg, pc, pw = models["B"]
+    prompts = [random_tokens(n, cfg.vocab_size, 300 + i) for i, n in enumerate((40, 23, 57, 9, 31))]
+    n_new = 24
+    expected = [plain_greedy(pc, pw, p, n_new) for p in prompts]
+    model = load_model(folder, dtype="float32")
+    model.kv_cache_init(256, max_sequences=4, page_size=8, kv_tokens=160)
+    eng = model.engine
+    eng.release(("seq", 0))
+    sched = Scheduler(eng, max_batch_tokens=48, prefill_chunk=16, n_ctx=256)
+    for i, p in enumerate(prompts):
+        sched.add(Request(("r", i), list(p), SamplerParams.greedy(), n_new, [], True))
+    done = sched.run()
+    assert [done[("r", i)].output for i in range(5)] == expected
+    assert sched.preemptions > 0
+    eng.cache.check()
+    assert eng.cache.free_pages() == [g.allocator.num_pages for g in eng.cache.groups]
+
+
 def test_prefix_reuse_context_full_and_errors(models):
     from purhie_b200.api import ERR_CONTEXT_FULL, ERR_INVALID_STATE, GenOptions, InferenceError, load_model
     from purhie_b200.sampling import SamplerParams
