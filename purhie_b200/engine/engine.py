@@ -136,6 +136,8 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.max_position = model.spec.max_position
         self.last_stats = StepStats()
+        # rows per tile of the products for many tokens (the tcgen05 pair kernel): a scheduler may end a step there
+        self.row_tile = 256 if self.dtype == torch.bfloat16 else None
         self._meta_host = [(None, None), (None, None)]
         self._pending_ring: List[Optional[PendingTokens]] = [None] * 4
         self._pending_turn = 0

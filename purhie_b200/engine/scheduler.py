@@ -73,10 +73,14 @@ class PlannedEntry:
 
 class Scheduler:
     def __init__(self, engine, *, max_batch_tokens: int = 2048, prefill_chunk: int = 512, max_running: Optional[int] = None,
-                 n_ctx: Optional[int] = None):
+                 n_ctx: Optional[int] = None, align_rows: Optional[int] = None):
         """``engine`` offers ``cache`` (a :class:`CacheManager`), ``step(entries)`` and ``sample(logits,
-        samplers)``, as :class:`purhie_b200.engine.Engine` does."""
+        samplers)``, as :class:`purhie_b200.engine.Engine` does.  ``align_rows`` (default: the engine's
+        ``row_tile``, if it names one): a prompt portion that is a cut anyway is shortened so that the step's rows
+        end on a multiple of it, because the products run in tiles of that many rows and a step of 544 rows costs
+        what one of 768 does."""
         self.engine = engine
+        self.align_rows = align_rows if align_rows is not None else getattr(engine, "row_tile", None)
         self.run_ahead = True                       # decode_ahead() may launch steps before the tokens of the last are read
         self.cache = engine.cache
         self.max_batch_tokens = max_batch_tokens
@@ -138,6 +142,16 @@ class Scheduler:
             best = min(best, room)
         return max(best, 0)
 
+    def _aligned(self, n: int, rest: int, used: int) -> int:
+        """The portion of n tokens (of rest that the request still has) after ``used`` rows of the step: when the
+        prompt goes on after it and the step would end past a multiple of align_rows, the portion ends there
+        instead, unless that takes more than half of it."""
+        a = self.align_rows
+        if not a or n >= rest or used + n < a:
+            return n
+        over = (used + n) % a
+        return n - over if over and n - over >= max(n // 2, 1) else n
+
     def _preempt(self, r: Request) -> None:
         self.cache.release(r.request_id)
         self.running.remove(r)
@@ -186,6 +200,7 @@ class Scheduler:
                 n = self._largest_portion(r, min(rest, budget, self.prefill_chunk), free)
                 if n <= 0:
                     continue
+                n = self._aligned(n, rest, self.max_batch_tokens - budget)
                 self._take(r, n, free)
                 plan.append(PlannedEntry(r, self._computed(r), n, n == rest))
                 budget -= n
@@ -206,6 +221,7 @@ class Scheduler:
                     n = min(free) * self.cache.page_size if free else n
                     if n <= 0:
                         break
+                n = self._aligned(n, rest, self.max_batch_tokens - budget)
                 self.waiting.popleft()
                 self.cache.add_request(r.request_id)
                 r.status = "running"

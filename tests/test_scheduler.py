@@ -234,3 +234,31 @@ def test_decoding_ahead_of_the_host_changes_no_output_and_ends():
             assert eng.cache.free_pages() == [pages] and eng.cache.slots.num_free == 4
         assert outs[0] == outs[1]
         assert outs[0]["d"][1] == STOP_EOG and outs[0]["b"][1] == STOP_MAX_TOKENS
+
+
+def test_a_cut_portion_ends_the_step_on_a_multiple_of_the_row_tile():
+    """With align_rows a portion that is a cut anyway is shortened so that the step's rows are a multiple of it;
+    the end of a prompt, a step below one tile and a cut that would lose more than half stay as they are, and the
+    outputs do not change."""
+    def run(align):
+        eng = FakeEngine(num_pages=4096, page_size=16, max_requests=40)
+        s = Scheduler(eng, max_batch_tokens=2048, prefill_chunk=512, align_rows=align)
+        for i in range(32):
+            s.add(Request(("d", i), [i + 1, i + 2], max_new_tokens=12))
+        s.step()                                                     # the 32 short prompts: 64 rows, all ends
+        s.add(Request("long", [(7 * i) % 50 for i in range(1300)], max_new_tokens=2))
+        run_all(s, eng)
+        return s, eng
+    s0, e0 = run(None)
+    s1, e1 = run(256)
+    sizes = lambda eng: [sum(n for _, n, _ in b) for b in eng.batches]
+    assert sizes(e0)[1:4] == [32 + 512, 32 + 512, 32 + 276]
+    assert sizes(e1)[1:4] == [512, 512, 32 + 340]                    # 480 + 32 twice, then the prompt's end as it is
+    for rid in s0.finished:
+        assert s0.finished[rid].output == s1.finished[rid].output
+    # below one tile nothing is cut; a cut that would take more than half is not made
+    eng = FakeEngine(num_pages=4096, page_size=16, max_requests=4)
+    s = Scheduler(eng, max_batch_tokens=2048, prefill_chunk=100, align_rows=256)
+    s.add(Request("p", [1] * 1000, max_new_tokens=1))
+    s.step(); s.step(); s.step()
+    assert [sum(n for _, n, _ in b) for b in eng.batches] == [100, 100, 100]
