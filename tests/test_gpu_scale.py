@@ -3,8 +3,9 @@
 The tiny configurations of the other tests leave paths untouched that only real sizes reach: a decode row whose
 context is cut into more splits than it has blocks to fill, products on pairs of CTAs, K in parts, attention
 tiles shared by several CTAs.  Two layers of an 8B-class shape (hidden 4096, 32 query heads over 8 kv heads of
-128, feed-forward 12288) with random weights: whatever way the tokens are fed, the bfloat16 engine must stay as
-close to the float32 engine as it is for a whole prompt.
+128, feed-forward 12288), of a 0.6B-class shape (hidden 1024 under a query width of 2048, tied embeddings) and of a
+32B-class shape (hidden 5120, groups of eight query heads, feed-forward 25600) with random weights: whatever way the
+tokens are fed, the bfloat16 engine must stay as close to the float32 engine as it is for a whole prompt.
 """
 import pytest
 import torch
@@ -14,17 +15,21 @@ pytestmark = pytest.mark.gpu
 SHAPE = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_layers=2, num_attention_heads=32,
              num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=32000, rms_norm_eps=1e-6,
              rope_theta=1000000.0, max_position_embeddings=8192, tie_word_embeddings=False, attention_bias=False)
+SHAPES = {"8b": SHAPE,
+          "0.6b": dict(SHAPE, hidden_size=1024, num_attention_heads=16, intermediate_size=3072, tie_word_embeddings=True),
+          "32b": dict(SHAPE, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)}
 
 
 def rel(a, b):
     return float((a.double() - b.double()).norm() / b.double().norm())
 
 
-def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt():
+@pytest.mark.parametrize("shape", sorted(SHAPES))
+def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt(shape):
     from purhie_b200.api import load_model_random
     from purhie_b200.config import Qwen3Config
     from purhie_b200.engine import Engine, StepEntry
-    cfg = Qwen3Config.from_dict(SHAPE)
+    cfg = Qwen3Config.from_dict(SHAPES[shape])
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, cfg.vocab_size, (2700,), generator=g).tolist()
     others = [torch.randint(0, cfg.vocab_size, (n + 24,), generator=g).tolist() for n in (17, 300, 1000, 2047, 64, 129, 700)]
