@@ -29,7 +29,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
 LIBRARIES: Dict[str, dict] = {
     "core": {
         "sources": ["elementwise.cu", "qk_norm_rope.cu", "attention_generic.cu", "gemm_simple.cu", "sampling.cu",
-                    "core_lib.cu"],
+                    "random_fill.cu", "core_lib.cu"],
+        "deps": ["../weights/random.h"],
         "flags": [],
         "link": [],
     },
@@ -43,6 +44,23 @@ LIBRARIES: Dict[str, dict] = {
         "sources": ["gemm_tcgen05.cu"],
         "flags": [],
         "link": [],
+    },
+    # the host library: configuration, weights, parts, cache manager, step function, scheduler, samplers and the C
+    # API (api/inference.h); it opens the kernel libraries above by need, from the folder it is loaded from
+    "qengine": {
+        "sources": ["../host/device.cpp", "../config/config.cpp", "../weights/safetensors.cpp", "../weights/weights.cpp",
+                    "../parts/registry.cpp", "../parts/linear.cpp", "../parts/norm.cpp", "../parts/rotary.cpp",
+                    "../parts/attention.cpp", "../parts/feed_forward.cpp", "../parts/embedding.cpp", "../parts/block.cpp",
+                    "../parts/model.cpp", "../cache/cache.cpp", "../sampling/sampler.cpp", "../engine/engine.cpp",
+                    "../engine/scheduler.cpp", "../api/capi.cpp", "../api/capi_generate.cpp", "../api/test_hooks.cpp",
+                    "../api/test_hooks_host.cpp"],
+        "deps": ["../host/common.h", "../host/json.h", "../host/device.h", "../config/config.h", "../weights/safetensors.h",
+                 "../weights/weights.h", "../weights/random.h", "../parts/parts.h", "../parts/linear.h", "../parts/model.h",
+                 "../cache/cache.h", "../sampling/sampler.h", "../engine/engine.h", "../engine/scheduler.h",
+                 "../api/inference.h", "../api/capi_internal.h"],
+        "flags": ["-Xcompiler", "-ffp-contract=off"],
+        "link": ["-ldl"],
+        "file_name": "libqengine.so",
     },
     # decode attention with its scratch in a fixed device array, for callers that cannot allocate
     "decode_static": {
@@ -125,8 +143,12 @@ def _run_with_heartbeat(cmds: List[List[str]], what: str) -> None:
             raise BuildError(f"command failed ({p.returncode}): {' '.join(c)}\n{out}")
 
 
+def library_file(name: str) -> str:
+    return LIBRARIES[name].get("file_name", f"libpurhie_{name}.so")
+
+
 def library_path(name: str) -> str:
-    return os.path.join(build_dir(), f"libpurhie_{name}.so")
+    return os.path.join(build_dir(), library_file(name))
 
 
 def build_library(name: str, verbose: bool = True) -> str:
@@ -136,7 +158,7 @@ def build_library(name: str, verbose: bool = True) -> str:
     srcs = [os.path.join(CSRC, s) for s in spec["sources"]]
     hdrs = [os.path.join(CSRC, h) for h in _HEADERS + spec.get("deps", [])]
     flags = ARCH_FLAGS + COMMON_FLAGS + spec["flags"]
-    so = os.path.join(out_dir, f"libpurhie_{name}.so")
+    so = os.path.join(out_dir, library_file(name))
     stamp = so + ".stamp"
     digest = _digest(srcs + hdrs, flags + spec["link"])
     if os.path.exists(so) and os.path.exists(stamp):
@@ -145,11 +167,13 @@ def build_library(name: str, verbose: bool = True) -> str:
                 return so
     nvcc = find_nvcc()
     if verbose:
-        _log(f"compiling the '{name}' kernels for sm_100a ({', '.join(spec['sources'])}) into {out_dir}")
+        what = "host library" if name == "qengine" else "kernels for sm_100a"
+        _log(f"compiling the '{name}' {what} ({len(srcs)} files) into {out_dir}")
     t0 = time.time()
     objs, cmds = [], []
     for s in srcs:
         o = os.path.join(out_dir, f"{name}_{os.path.basename(s)}.{os.getpid()}.o")
+        s = os.path.normpath(s)
         objs.append(o)
         cmds.append([nvcc] + flags + ["-I", CSRC, "-c", s, "-o", o])
     try:
@@ -165,7 +189,7 @@ def build_library(name: str, verbose: bool = True) -> str:
             if os.path.exists(o):
                 os.unlink(o)
     if verbose:
-        _log(f"'{name}' kernels ready ({time.time() - t0:.0f} s)")
+        _log(f"'{name}' ready ({time.time() - t0:.0f} s)")
     return so
 
 

@@ -1,7 +1,8 @@
-"""Python face of the tensor-core attention kernels (attention_flash.cu).
+"""Python face of the tensor-core attention kernels, for the kernels' own tests and measurements.
 
-A step's rows go two ways: segments of one token (decoding) through the split-key kernel, every other
-segment (a portion of a prompt) through the tiled kernel.  Both read keys and values from the pages.
+A step's rows go two ways: segments of one token (decoding) through a split-key kernel, every other
+segment (a portion of a prompt) through a tiled kernel.  Both read keys and values from the pages.  The
+engine chooses among them, and the number of splits, in parts/attention.cpp.
 """
 from __future__ import annotations
 
@@ -187,34 +188,3 @@ def decode_bulk(q, k_base, v_base, page_stride, page_size, num_pages, block_tabl
          row_seg.data_ptr(), positions.data_ptr(), None if part_o is None else part_o.data_ptr(),
          None if part_ml is None else part_ml.data_ptr(), out.data_ptr(), num_heads, num_kv_heads, head_dim, splits,
          int(window or 0), float(scale), max_ctas, error_flag(q.device).data_ptr(), ops._stream())
-
-
-def attention(q, cache, group, ctx, out, *, num_heads, num_kv_heads, head_dim, window, scale) -> None:
-    """All rows of the step: q [T, HQ, D] bfloat16 -> out [T, HQ * D] bfloat16."""
-    for name, t in (("q", q), ("out", out), ("k", cache.k_base)):
-        if t.dtype != torch.bfloat16:
-            raise KernelError(f"attention_flash: {name} must be bfloat16")
-    if ctx.n_q_tiles and ctx.n_q_tiles_large and tc5_supports(head_dim, cache.page_size) and cache.num_pages \
-            and ctx.extra.get("prefill_kernel") != "mma_sync":
-        longest = ctx.prefill_max_ctx or max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n > 1)
-        splits = ctx.extra.get("prefill_splits") or tc5_splits(ctx.n_q_tiles_large, num_heads, longest, _sms(q.device), window)
-        prefill_tc5(q, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
-                    group.block_table, ctx.seg_start, ctx.seg_ctx_len, ctx.q_tile_large_seg, ctx.q_tile_large_first,
-                    ctx.n_q_tiles_large, out, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-                    window=window, scale=scale, splits=splits, workspace=ctx.workspace)
-    elif ctx.n_q_tiles:
-        prefill(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.seg_start,
-                ctx.seg_ctx_len, ctx.q_tile_seg, ctx.q_tile_first, ctx.n_q_tiles, out, num_heads=num_heads,
-                num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale)
-    if ctx.n_decode_rows:
-        if ctx.extra.get("decode_kernel") == "cp_async" or not bulk_supports(cache.page_size) or not cache.num_pages:
-            splits = decode_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx, _sms(q.device), window)
-            decode(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, group.block_table, ctx.decode_rows,
-                   ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace, num_heads=num_heads,
-                   num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale, splits=splits)
-        else:
-            splits = bulk_splits(ctx.n_decode_rows, num_kv_heads, ctx.decode_max_ctx, _sms(q.device), window)
-            decode_bulk(q, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages, group.block_table,
-                        ctx.decode_rows, ctx.n_decode_rows, ctx.row_seg, ctx.positions, out, ctx.workspace,
-                        num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, window=window, scale=scale,
-                        splits=splits)

@@ -1,0 +1,147 @@
+// Device memory, scratch space and the kernel libraries, as the host library sees them.
+//
+// All device memory is plain cudaMalloc memory owned by a DeviceBuffer; a Workspace hands out named scratch
+// tensors that keep their address from step to step (what a captured CUDA graph needs).  The kernels live in
+// separate shared objects (libpurhie_core.so, libpurhie_flash.so, libpurhie_gemm100.so) that are opened by
+// need from the folder this library was loaded from: a float32 model never touches the tensor-core libraries.
+// A missing library is an error that says how to build it; there is no other implementation to fall back to.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.h"
+
+namespace qe {
+
+#define QE_CUDA(expr)                                                                                  \
+    do {                                                                                               \
+        cudaError_t qe_e_ = (expr);                                                                    \
+        if (qe_e_ != cudaSuccess)                                                                      \
+            throw ::qe::Error(qe_e_ == cudaErrorMemoryAllocation ? ::qe::kOutOfMemory : ::qe::kKernelLaunch, \
+                              std::string(#expr) + ": " + cudaGetErrorString(qe_e_));                 \
+    } while (0)
+
+// Owns one cudaMalloc allocation.
+class QE_API DeviceBuffer {
+public:
+    DeviceBuffer() = default;
+    explicit DeviceBuffer(size_t bytes);
+    ~DeviceBuffer();
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    DeviceBuffer(DeviceBuffer&& o) noexcept : p_(o.p_), n_(o.n_) { o.p_ = nullptr; o.n_ = 0; }
+    DeviceBuffer& operator=(DeviceBuffer&& o) noexcept;
+    void* data() const { return p_; }
+    size_t bytes() const { return n_; }
+    void reset();
+private:
+    void* p_ = nullptr;
+    size_t n_ = 0;
+};
+
+// Page-locked host memory.
+class QE_API PinnedBuffer {
+public:
+    PinnedBuffer() = default;
+    explicit PinnedBuffer(size_t bytes);
+    ~PinnedBuffer();
+    PinnedBuffer(const PinnedBuffer&) = delete;
+    PinnedBuffer& operator=(const PinnedBuffer&) = delete;
+    void* data() const { return p_; }
+    size_t bytes() const { return n_; }
+    void ensure(size_t bytes);          // grows (contents are lost)
+private:
+    void* p_ = nullptr;
+    size_t n_ = 0;
+};
+
+// Device tensors that somebody keeps for good (weights and what parts derive from them).
+class QE_API DeviceArena {
+public:
+    Tensor alloc(DType dtype, std::vector<int64_t> shape);
+    void release(const Tensor& t);      // give one allocation back early (a temporary made while binding)
+    size_t bytes() const { return bytes_; }
+private:
+    std::map<void*, DeviceBuffer> bufs_;
+    size_t bytes_ = 0;
+};
+
+// Scratch tensors by name, reused from step to step and grown on demand.  A tensor of a given name keeps its
+// address as long as requests do not outgrow it; `frozen` turns growth into an error (a captured graph points
+// at these addresses).
+class QE_API Workspace {
+public:
+    Workspace() = default;
+    Tensor get(const std::string& name, std::vector<int64_t> shape, DType dtype);
+    size_t bytes() const;
+    bool frozen = false;
+    cudaStream_t stream = nullptr;      // growing waits for this stream before the old block is freed
+private:
+    std::map<std::string, DeviceBuffer> bufs_;
+};
+
+// ---- kernel libraries ---------------------------------------------------------------------------------------
+// Launcher prototypes (see the .cu files under csrc/).  Every launcher returns 0 or a status with a text.
+struct CoreKernels {
+    int (*embed_gather)(const void*, int, const int32_t*, float*, int, int, int, cudaStream_t);
+    int (*add_rmsnorm)(float*, const void*, int, int, long long, const float*, float, const int32_t*, int, int, void*, int,
+                       int, cudaStream_t);
+    int (*swiglu)(const void*, int, int, long long, void*, int, int, int, cudaStream_t);
+    int (*cast)(const void*, int, void*, int, long long, cudaStream_t);
+    int (*qk_norm_rope_kv_write)(const void*, int, int, long long, const float*, const float*, const float*, float,
+                                 const float*, int, int, const int32_t*, const int32_t*, void*, int, void*, void*, int,
+                                 long long, int, int, int, int, int, int, cudaStream_t);
+    int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
+                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, cudaStream_t);
+    int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
+    int (*argmax)(const float*, int, int, int32_t*, cudaStream_t);
+    int (*sample_temperature)(const float*, int, int, const float*, const double*, float, int32_t*, cudaStream_t);
+    int (*sample_chain)(const float*, int, int, const void*, int32_t*, cudaStream_t);
+    int (*sample_chain_max_k)(void);
+    int (*random_fill)(void*, int, long long, unsigned long long, int, double, double, cudaStream_t);
+    const char* (*last_error)(void);
+};
+struct FlashKernels {
+    int (*prefill)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*,
+                   const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, float, cudaStream_t);
+    int (*decode)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*, int,
+                  const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, float, cudaStream_t);
+    int (*decode_bulk)(const void*, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*, int,
+                       const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, float, int, int*,
+                       cudaStream_t);
+    int (*prefill_tc5)(const void*, int, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*,
+                       const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, float, int, float*,
+                       float*, int*, cudaStream_t);
+    const char* (*last_error)(void);
+};
+struct GemmKernels {
+    int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, int*, cudaStream_t);
+    int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int*, cudaStream_t);
+    const char* (*last_error)(void);
+};
+
+// Folder the kernel libraries are opened from: set_library_dir(), else $PURHIE_B200_LIB_DIR, else the folder
+// this library itself was loaded from.
+QE_API void set_library_dir(const std::string& dir);
+QE_API std::string library_dir();
+QE_API const CoreKernels& core_kernels();
+QE_API const FlashKernels& flash_kernels();
+QE_API const GemmKernels& gemm_kernels();
+QE_API void require_library(const std::string& name);      // "core", "flash", "gemm100": open it now
+QE_API extern long long g_launches;                          // launcher calls so far (for the bench's count)
+
+// Run a launcher; a non-zero status becomes a KernelError with the library's text.
+#define QE_LAUNCH(lib, call)                                                                     \
+    do {                                                                                         \
+        ::qe::g_launches++;                                                                      \
+        if ((call) != 0) throw ::qe::KernelError((lib).last_error());                           \
+    } while (0)
+
+QE_API int sm_count();                                      // of the current device
+
+}  // namespace qe

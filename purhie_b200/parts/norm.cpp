@@ -1,0 +1,40 @@
+// RMSNorm with the residual add folded in.
+//
+// y = v * rsqrt(mean(v^2) + eps) * w, v = x + pending addend; the weight multiplies after normalising (plain w,
+// not 1 + w).  Reference: src/gpu_ops.hip:24-56 (add + norm in one kernel), src/qwen_ops.cpp:8-13.
+#include "parts.h"
+
+namespace qe {
+
+// params: size, eps, names{weight}.
+class RMSNorm : public Norm {
+public:
+    RMSNorm(const Json& p, BuildContext& b) : Norm(p, b), size_(p.at("size").as_int()), eps_(p.at("eps").as_double()) {
+        if (size_ < 1 || !(eps_ > 0)) throw ConfigError("rmsnorm: size must be positive and eps > 0");
+    }
+    std::vector<TensorSpec> tensor_specs() const override { return {{name_of("weight"), {size_}, Role::Vector, Init::Scale}}; }
+    void bind(WeightSource& src) override { weight_ = src.fetch(name_of("weight")); }
+
+    Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
+        const int n = rows ? n_rows : ctx.T;
+        Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
+        const CoreKernels& k = core_kernels();
+        const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
+        QE_LAUNCH(k, k.add_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
+                                   pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
+                                   (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1, ctx.stream));
+        if (!rows) stream.clear();
+        return out;
+    }
+
+private:
+    int64_t size_;
+    double eps_;
+    Tensor weight_;
+};
+
+void register_norm_parts() {
+    register_part("norm", "rmsnorm", [](const Json& p, BuildContext& b) { return std::make_shared<RMSNorm>(p, b); });
+}
+
+}  // namespace qe

@@ -19,6 +19,9 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_si
               rope_theta=1e6, rms_norm_eps=1e-5, tie_word_embeddings=False, attention_bias=True,
               use_sliding_window=True, sliding_window=24, max_window_layers=1)
 TINY_B_INIT = dict(seed=1, std=0.03, scale_low=0.8, scale_high=1.2, page_size=8)
+# The second configuration as the benchmark description writes it: no attention bias, attention over all keys.
+TINY_B0 = {k: v for k, v in TINY_B.items() if k not in ("use_sliding_window", "sliding_window", "max_window_layers")}
+TINY_B0["attention_bias"] = False
 
 # A third shape for the fast kernels: head size 64 and 128 are what they take.
 TINY_C = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=160, intermediate_size=352,
@@ -27,10 +30,11 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_si
               layer_types=["full_attention", "sliding_attention"], sliding_window=40)
 TINY_C_INIT = dict(seed=7, std=0.05, scale_low=0.7, scale_high=1.3, page_size=16)
 
-TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+TINY = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "B0": (TINY_B0, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
 
 
 def make_model(folder, cfg_dict, init, dtype="float32"):
+    """Write a random model folder (matrices stored in ``dtype``); returns the typed configuration."""
     from purhie_b200.config import Qwen3Config
     from purhie_b200.weights import write_random_model
     cfg = Qwen3Config.from_dict(cfg_dict)
@@ -48,14 +52,17 @@ def rel_err(got, ref):
     return ((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()
 
 
-def same_top1_or_near_tie(got, ref, gap=0.1):
-    """Rows whose argmax differs must be near-ties in the reference: the reference's rule for reduced
-    precision (tests/seq_verify.cpp:64-99 in the reference: a first difference only at a gap < 0.1)."""
+def same_top1_or_near_tie(got, ref, tol):
+    """Rows whose argmax differs must be near-ties in the reference (the reference's rule for reduced precision,
+    tests/seq_verify.cpp:64-99 there, accepts a first difference only at a small gap).  The gap allowed here is what
+    the granted tolerance can explain and no more: the error bound is ``tol`` of the largest logit of the request, so
+    two logits can swap only if they were within twice that."""
     got, ref = got.double().cpu(), ref.double().cpu()
     bad = []
+    allowed = 2.0 * tol * ref.abs().max().item()
     for i in range(ref.shape[0]):
         a, b = int(got[i].argmax()), int(ref[i].argmax())
-        if a != b and (ref[i, b] - ref[i, a]).item() > gap * max(1.0, ref[i].abs().max().item()):
+        if a != b and (ref[i, b] - ref[i, a]).item() > allowed:
             bad.append(i)
     return bad
 
@@ -181,6 +188,6 @@ def engine_runner(engine):
             if not engine.has_request(rid):
                 engine.add_request(rid)
         lg = engine.step([StepEntry(rid, toks, want) for rid, toks, want in entries])
-        return None if lg is None else lg.float().cpu()
+        return None if lg is None else torch.from_numpy(lg.copy())
 
     return step, engine.release
