@@ -28,11 +28,6 @@ SamplerParams to_params(const sampler_params& p) {
 }  // namespace capi
 }  // namespace qe
 
-struct sampler {
-    Sampler s;
-    explicit sampler(const SamplerParams& p) : s(p) {}
-};
-
 namespace qe {
 namespace capi {
 Engine& need_engine(inference_model* m) {
@@ -307,6 +302,13 @@ API void inference_kv_cache_free(inference_model_t* m) {
     m->n_ctx = 0;
 }
 
+API int inference_synchronize(inference_model_t* m) {
+    return guarded([&] {
+        need_engine(m).synchronize();
+        return 0;
+    });
+}
+
 API void inference_set_seed(inference_model_t* m, unsigned int seed) { if (m) m->seed = seed; }
 API void inference_set_prefill_batch(inference_model_t* m, int n) { if (m) m->prefill_batch = n < 1 ? 1 : n; }
 
@@ -316,6 +318,7 @@ API int inference_batch_size(const inference_model_t* m) { return m ? m->max_seq
 API const char* inference_model_name(const inference_model_t* m) { return m ? m->name.c_str() : ""; }
 API int inference_vocab_size(const inference_model_t* m) { return m ? (int)m->decoder->spec().vocab_size : 0; }
 API int inference_hidden_size(const inference_model_t* m) { return m ? (int)m->decoder->spec().hidden_size : 0; }
+API int inference_max_position(const inference_model_t* m) { return m ? (int)m->decoder->spec().max_position : 0; }
 
 // ---- sequences -----------------------------------------------------------------------------------------------------------------
 API int inference_seq_new(inference_model_t* m) {

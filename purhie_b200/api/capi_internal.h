@@ -76,6 +76,11 @@ struct inference_model {
     std::map<long long, std::unique_ptr<qe::GenRequest>> done;
 };
 
+struct sampler {
+    qe::Sampler s;
+    explicit sampler(const qe::SamplerParams& p) : s(p) {}
+};
+
 struct inference_stream {
     inference_model* model = nullptr;
     int seq = 0;

@@ -89,6 +89,9 @@ int inference_kv_cache_init_ex(inference_model_t* model, int n_ctx, int max_sequ
                                const char* engine_options_json);
 void inference_kv_cache_free(inference_model_t* model);
 
+/* Wait until everything the model has launched is done; reports a kernel that gave up on a wait. */
+int inference_synchronize(inference_model_t* model);
+
 void inference_set_seed(inference_model_t* model, unsigned int seed);      /* for inference_generate_ex without params */
 void inference_set_prefill_batch(inference_model_t* model, int n_tokens); /* most tokens per pass of a prefill (default 1024) */
 
@@ -229,6 +232,7 @@ int inference_batch_size(const inference_model_t* model);     /* most sequences 
 const char* inference_model_name(const inference_model_t* model);
 int inference_vocab_size(const inference_model_t* model);
 int inference_hidden_size(const inference_model_t* model);
+int inference_max_position(const inference_model_t* model);   /* the longest sequence the model's configuration allows */
 
 #ifdef __cplusplus
 }

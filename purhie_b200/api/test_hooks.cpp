@@ -203,6 +203,25 @@ API int qe_random_tensor(const char* name, const char* init, long long n, uint64
     });
 }
 
+// ---- samplers ----------------------------------------------------------------------------------------------------------
+// Which device kernel gives what this sampler gives on the host: "greedy", "temperature", "chain", or "" (none).
+API const char* qe_sampler_device_mode(sampler_t* s) {
+    switch (s->s.device_mode()) {
+        case Sampler::DeviceMode::Greedy: return "greedy";
+        case Sampler::DeviceMode::Temperature: return "temperature";
+        case Sampler::DeviceMode::Chain: return "chain";
+        default: return "";
+    }
+}
+API int qe_sampler_chain_max_k(void) { return Sampler::kChainMaxK; }
+// `draws` tokens sampled from one row of logits (none accepted); counts[token] is incremented for each.
+API int qe_sampler_histogram(sampler_t* s, const float* logits, int n_vocab, long long draws, long long* counts) {
+    return guarded([&] {
+        for (long long i = 0; i < draws; i++) counts[s->s.sample(logits, n_vocab)]++;
+        return 0;
+    });
+}
+
 // The kernel libraries a loaded model launches from, as a JSON list ("core", "flash", "gemm100"): a binding that
 // compiles libraries by need builds these before inference_kv_cache_init.
 API const char* qe_model_required_libraries(inference_model_t* m) {

@@ -135,6 +135,7 @@ _SIGNATURES = {
     "inference_kv_cache_init": (c_int, [_P, c_int]),
     "inference_kv_cache_init_ex": (c_int, [_P, c_int, c_int, c_int, c_longlong, c_char_p]),
     "inference_kv_cache_free": (None, [_P]),
+    "inference_synchronize": (c_int, [_P]),
     "inference_set_seed": (None, [_P, c_uint]),
     "inference_set_prefill_batch": (None, [_P, c_int]),
     "inference_reset": (None, [_P]),
@@ -175,6 +176,7 @@ _SIGNATURES = {
     "inference_model_name": (c_char_p, [_P]),
     "inference_vocab_size": (c_int, [_P]),
     "inference_hidden_size": (c_int, [_P]),
+    "inference_max_position": (c_int, [_P]),
     # for tests and tools
     "qe_config_read": (c_char_p, [c_char_p]),
     "qe_config_load": (c_char_p, [c_char_p]),
@@ -188,6 +190,9 @@ _SIGNATURES = {
     "qe_safetensors_read": (c_longlong, [c_char_p, c_char_p, c_void_p, c_longlong]),
     "qe_device_dtype": (c_char_p, [c_char_p, c_char_p, c_char_p]),
     "qe_random_tensor": (c_int, [c_char_p, c_char_p, c_longlong, c_uint64, c_double, c_double, c_double, POINTER(c_float)]),
+    "qe_sampler_device_mode": (c_char_p, [_P]),
+    "qe_sampler_chain_max_k": (c_int, []),
+    "qe_sampler_histogram": (c_int, [_P, POINTER(c_float), c_int, c_longlong, POINTER(c_longlong)]),
     "qe_model_required_libraries": (c_char_p, [_P]),
     "qe_engine_info": (c_char_p, [_P]),
     "qe_engine_cache_check": (c_int, [_P]),

@@ -57,6 +57,23 @@ class Sampler:
         row = np.ascontiguousarray(np.asarray(logits, dtype=np.float32))
         return native.lib().sampler_sample(self._h, row.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), int(row.size))
 
+    def histogram(self, logits, draws: int) -> np.ndarray:
+        """How often each token comes out of ``draws`` draws from one row (none of them accepted)."""
+        row = np.ascontiguousarray(np.asarray(logits, dtype=np.float32))
+        counts = np.zeros(row.size, dtype=np.int64)
+        native.check(native.lib().qe_sampler_histogram(self._h, row.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), int(row.size),
+                                                       int(draws), counts.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong))))
+        return counts
+
+    def device_mode(self) -> Optional[str]:
+        """"greedy", "temperature" or "chain" (top-k on, at most ``chain_max_k()``) when a device kernel gives the same
+        result as the chain on the host, else None (penalties, top-p or min-p without top-k)."""
+        return native.lib().qe_sampler_device_mode(self._h).decode() or None
+
+    @staticmethod
+    def chain_max_k() -> int:
+        return native.lib().qe_sampler_chain_max_k()
+
     def accept(self, token: int) -> None:
         native.lib().sampler_accept(self._h, int(token))
 

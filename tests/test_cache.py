@@ -3,7 +3,8 @@ import random
 
 import pytest
 
-from purhie_b200.cache import CacheManager, CacheNeed, OutOfPages, OutOfSlots, PageAllocator, SlotAllocator
+from purhie_b200.cache import CacheManager, CacheNeed, CheckError, OutOfPages, OutOfSlots, PageAllocator, SlotAllocator
+from purhie_b200.native import InferenceError
 
 
 def test_allocator_hands_out_each_page_once_and_reuses_the_last_freed():
@@ -16,7 +17,7 @@ def test_allocator_hands_out_each_page_once_and_reuses_the_last_freed():
     a.free([p[1]])
     assert a.alloc(1) == [p[1]]                 # reuse starts with the page freed last
     a.free(p)
-    with pytest.raises(ValueError):
+    with pytest.raises(CheckError):
         a.free([p[0]])                          # freed twice
     a.check()
 
@@ -35,7 +36,7 @@ def test_slots():
     with pytest.raises(OutOfSlots):
         s.alloc()
     s.free(x)
-    with pytest.raises(ValueError):
+    with pytest.raises(CheckError):
         s.free(x)
     assert s.alloc() == x
     s.check()
@@ -49,7 +50,7 @@ def needs_two_groups():
 
 def test_groups_are_formed_by_geometry_and_policy():
     m = CacheManager(needs_two_groups(), page_size=8, num_pages=[10, 6], max_requests=3)
-    assert [(g.window, g.entries) for g in m.groups] == [(None, [0]), (24, [1, 3])]
+    assert [(g["window"], g["entries"]) for g in m.groups] == [(None, [0]), (24, [1, 3])]
     assert m.state_entries == [4]
     assert m.entry_group == {0: 0, 1: 1, 3: 1}
 
@@ -69,13 +70,13 @@ def test_pages_grow_one_block_at_a_time_and_window_pages_return():
         first_needed = max(0, total - 24 + 1) // 8
         t = m.block_table("a", 1)
         assert all(p == -1 for p in t[:first_needed]) and all(p >= 0 for p in t[first_needed:])
-    assert m.groups[1].allocator.num_used == len(m.block_table("a", 1)) - max(0, total - 24 + 1) // 8
+    assert m.groups[1]["used"] == len(m.block_table("a", 1)) - max(0, total - 24 + 1) // 8
     slots = m.token_slots("a", 0, 60, 4)
     assert len(set(slots)) == 4
     with pytest.raises(RuntimeError):
         m.token_slots("a", 1, 0, 1)             # that page was given back
     m.release("a")
-    assert m.free_pages() == [16, 16] and m.slots.num_free == 2
+    assert m.free_pages() == [16, 16] and m.free_slots == 2
     m.check()
 
 
@@ -98,7 +99,7 @@ def test_truncate_gives_back_whole_pages_past_the_length():
     m.reserve("a", 14); m.advance("a", 14)
     m.truncate("a", 5)
     assert m.length("a") == 5 and len(m.block_table("a", 0)) == 2 and m.free_pages() == [6]
-    with pytest.raises(ValueError):
+    with pytest.raises(InferenceError):
         m.truncate("a", 9)
     m.check()
 
@@ -150,7 +151,7 @@ class _null:
 def test_slots_of_a_long_portion_are_those_of_its_tokens_one_by_one():
     """Long portions are mapped page by page; the result is what mapping every token alone gives, also across pages
     that a window has passed (which must raise either way)."""
-    cm = CacheManager([CacheNeed.pages(1, 8, None), CacheNeed.pages(1, 8, 40)], 16, 64, 2)
+    cm = CacheManager([CacheNeed.pages(1, 8, None), CacheNeed.pages(1, 8, 40)], 16, [64, 64], 2)
     cm.add_request("a")
     cm.reserve("a", 300)
     for g in (0, 1):

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 from plain import qwen3_plain as P
-from purhie_b200.sampling import MT19937_64, Sampler, SamplerParams
+from purhie_b200.sampling import Sampler, SamplerParams
 from helpers import TINY_A, TINY_A_INIT, TINY_B, TINY_B_INIT, make_model, random_tokens
 
 GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "ref_ops.json")))
@@ -81,18 +81,19 @@ def test_layer_windows_from_config_keys():
 
 
 # ---- sampler -------------------------------------------------------------------------------------------
-
-def test_mt19937_64_is_the_standard_generator():
-    g = MT19937_64(5489)
-    for _ in range(9999):
-        g.next_u64()
-    assert g.next_u64() == 9981545732273789042              # the C++ standard's check value
-
+# The sampler under test is the host library's (sampling/sampler.cpp); the golden chains were drawn by the reference's
+# own src/sampler.cpp with equal seeds, so equal tokens mean equal draws from the same generator.
 
 def test_greedy_lowest_id_wins_ties():
     l = np.array(GOLD["samp_logits"], dtype=np.float32)
     assert Sampler(SamplerParams.greedy()).sample(l) == GOLD["samp_greedy"] == 11
     assert P.greedy(l) == 11
+
+
+def test_defaults_are_the_reference_s():
+    d = SamplerParams.defaults()
+    assert (round(d.temperature, 6), d.top_k, round(d.top_p, 6), round(d.min_p, 6), d.repeat_penalty, d.repeat_last_n, d.seed,
+            d.presence_penalty) == (0.8, 40, 0.95, 0.05, 1.0, 64, 0, 0.0)           # src/sampler.cpp:181-192
 
 
 @pytest.mark.parametrize("name,params", [
@@ -114,19 +115,18 @@ def test_sampler_chain_draws_the_reference_tokens(name, params):
 
 
 def test_temperature_distribution():
+    """200,000 draws against the exact probabilities, to 0.006: the reference's own bar (tests/sampler_verify.cpp:1-4)."""
     l = np.array(GOLD["samp_logits"], dtype=np.float32)
     p = P.temperature_probabilities(l, 0.7)
     s = Sampler(SamplerParams.pure_temperature(0.7, seed=2))
-    counts = np.zeros_like(p)
-    n = 20000
-    for _ in range(n):
-        counts[s.sample(l)] += 1
-    assert np.abs(counts / n - p).max() < 0.012
+    n = 200000
+    counts = s.histogram(l, n)
+    assert counts.sum() == n and np.abs(counts / n - p).max() < 0.006
     # which kernel samples what: plain temperature, the chain with top-k on; the host keeps top-p without top-k,
     # more candidates than the kernel holds, and penalties
     assert s.device_mode() == "temperature" and Sampler(SamplerParams()).device_mode() == "chain"
     assert Sampler(SamplerParams(top_k=0)).device_mode() is None
-    assert Sampler(SamplerParams(top_k=Sampler.CHAIN_MAX_K + 1)).device_mode() is None
+    assert Sampler(SamplerParams(top_k=Sampler.chain_max_k() + 1)).device_mode() is None
     pen = Sampler(SamplerParams(repeat_penalty=1.1))
     pen.accept(3)
     assert pen.device_mode() is None and Sampler(SamplerParams(temperature=0.0)).device_mode() == "greedy"
@@ -138,5 +138,6 @@ def test_reset_reseeds_and_forgets():
     s = Sampler(SamplerParams(seed=4, repeat_penalty=1.2))
     a = [s.sample(l) for _ in range(5)]
     s.accept(3)
+    assert s.device_mode() is None                      # a token in the window: the penalty is live
     s.reset()
-    assert [s.sample(l) for _ in range(5)] == a and not s.history
+    assert [s.sample(l) for _ in range(5)] == a and s.device_mode() == "chain"
