@@ -3,11 +3,13 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
 
-Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on
-the device over exactly K decode steps after W warm-up steps; ``e2e`` is the same through the Python entry
-point (purhie_b200.api) with host token ids in and sampled tokens out every step; ``prefill`` is one
-2,048-token prompt; ``roofline`` is the decode step's bytes (every weight once plus the live requests'
-cache) over its time; ``points`` holds decode at batch 1 and 64 and a mixed step (32 decoded tokens beside a 512-token prompt chunk).  Token ids are uniform random (synthetic).
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on the
+device (CUDA events on the engine's stream) over exactly K decode steps after W warm-up steps, each step fed its
+token ids from the host and ending in the greedy sampling kernel; ``e2e`` is the same through the Python entry point
+(purhie_b200.api: streams, host token ids in and sampled tokens out every step) by the wall clock; ``prefill`` is
+one 2,048-token prompt from submit to logits; ``roofline`` is the decode step's bytes (every weight once plus the
+live requests' cache) over its time; ``points`` holds decode at batch 1 and 64 and a mixed step (32 decoded tokens
+beside a 512-token prompt chunk).  Token ids are uniform random (synthetic).
 """
 import argparse
 import json
@@ -29,19 +31,21 @@ QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, intermediate_
                  num_key_value_heads=8, tie_word_embeddings=True)
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, intermediate_size=25600, num_attention_heads=64,
                  num_key_value_heads=8)
-SHAPES = {"8b": ("Qwen3-8B", QWEN3_8B, 2, (1, 64)), "0.6b": ("Qwen3-0.6B", QWEN3_06B, 3, (1, 64)),
-          "32b": ("Qwen3-32B", QWEN3_32B, 4, (1, 32))}
+SHAPES = {"8b": ("Qwen3-8B", QWEN3_8B, 2, 0.02, (1, 64)), "0.6b": ("Qwen3-0.6B", QWEN3_06B, 3, 0.02, (1, 64)),
+          "32b": ("Qwen3-32B", QWEN3_32B, 4, 0.015, (1, 32))}
 CONTEXT, PREFIX, PREFILL_TOKENS = 4096, 2048, 2048
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def peaks():
+    """The roofline denominators: the measured copy bandwidth, and the cuBLAS bf16 rate as a burst (a kernel timed
+    alone, which is how the prefill is timed here) and sustained under the power cap."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
             d = json.load(open(path))
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
-                    "source": "measured"}
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]), "source": "measured"}
         except (ValueError, KeyError, OSError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
@@ -107,7 +111,7 @@ def main():
                     help="fewer layers than the configuration has (named in config); layer sizes stay")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the mixed step")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="run one phase only, with few launches around it (for profiling under ncu)")
     args = ap.parse_args()
@@ -118,55 +122,43 @@ def main():
         return 2
     args.warmup = max(args.warmup, 3)
 
-    import torch
+    import numpy as np
     from purhie_b200.api import GenOptions, load_model_random
     from purhie_b200.config import Qwen3Config
-    from purhie_b200.csrc import gemm100, ops
-    from purhie_b200.engine import StepEntry
+    from purhie_b200.engine import Engine, StepEntry
     from purhie_b200.sampling import SamplerParams
 
-    shape_name, shape, SEED, point_batches = SHAPES[args.shape]
+    shape_name, shape, SEED, STD, point_batches = SHAPES[args.shape]
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]
     cfg = Qwen3Config.from_dict(dict(shape, num_hidden_layers=args.layers))
     pk = peaks()
-    dev = "cuda:0"
-    model = load_model_random(cfg, SEED, "bfloat16", dev)
+    model = load_model_random(cfg, SEED, "bfloat16", std=STD)
     max_batch = args.batch if args.phase != "all" else max(max(point_batches), args.batch)
     if args.phase != "all":
         args.no_points = True
-    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 1, page_size=16,
-                        kv_tokens=max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64)
-    eng = model.engine
-    eng.release(("seq", 0))
-    g = torch.Generator().manual_seed(SEED)
-    ids = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
-
-    def timed(fn, reps):
-        ts = []
-        for _ in range(reps):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            s.record(); fn(); e.record()
-            torch.cuda.synchronize()
-            ts.append(s.elapsed_time(e))
-        ts.sort()
-        return ts[len(ts) // 2]
+    kv_tokens = max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64
+    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 2, page_size=16, kv_tokens=kv_tokens)
+    eng = Engine.attach(model)
+    rng = np.random.default_rng(SEED)
+    ids = lambda n: rng.integers(0, cfg.vocab_size, size=n).tolist()
+    median = lambda xs: sorted(xs)[len(xs) // 2]
 
     # ---- prefill of one 2,048-token prompt ----------------------------------------------------------
     prompt = ids(PREFILL_TOKENS)
 
     def prefill_once():
         eng.add_request("prefill")
-        eng.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+        ms = eng.time_step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
         eng.release("prefill")
+        return ms
 
     if args.phase == "decode":
         prefill_ms = float("nan")
     else:
         for _ in range(3 if args.phase == "all" else 1):
             prefill_once()
-        prefill_ms = timed(prefill_once, 5 if args.phase == "all" else 1)
+        prefill_ms = median([prefill_once() for _ in range(5 if args.phase == "all" else 1)])
     if args.phase == "prefill":
         print(json.dumps({"phase": "prefill", "ms": prefill_ms, "layers": args.layers}))
         return 0
@@ -174,42 +166,25 @@ def main():
     qw, kvw, D = cfg.q_width, cfg.kv_width, cfg.head_dim
     layer_mm = E * (qw + 2 * kvw) + qw * E + 3 * E * FF
     prefill_flops = cfg.num_hidden_layers * (2.0 * T * layer_mm + 4.0 * cfg.num_attention_heads * D * T * (T + 1) / 2) + 2.0 * V * E
+    tflops = prefill_flops / (prefill_ms * 1e-3) / 1e12
     prefill = {"value": round(T / prefill_ms * 1e3, 1), "tokens": T, "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "tflops": round(prefill_flops / (prefill_ms * 1e-3) / 1e12, 1), "peak": pk["source"]}
+               "frac": round(tflops / pk["bf16_tflops"], 4), "frac_of_sustained": round(tflops / pk["bf16_tflops_sustained"], 4),
+               "tflops": round(tflops, 1), "peak": pk["source"]}
 
     # ---- prefixes of 2,048 tokens for every request ---------------------------------------------------
     for i in range(max_batch):
         eng.add_request(i)
         eng.step([StepEntry(i, ids(PREFIX), [])])
-    torch.cuda.synchronize()
 
     weight_bytes = 2.0 * (cfg.num_hidden_layers * layer_mm + V * E)       # the embedding table is gathered, not streamed
     kv_bytes_per_token = 2.0 * 2 * cfg.num_hidden_layers * kvw
 
     def decode_run(batch, steps, warmup):
+        ctx0 = eng.length(0) + warmup
         toks = [ids(steps + warmup) for _ in range(batch)]
-        step_no = [0]
-
-        def one():
-            k = step_no[0]
-            step_no[0] += 1
-            eng.step([StepEntry(i, [toks[i][k]], [0]) for i in range(batch)])
-
-        for _ in range(warmup):
-            one()
-        torch.cuda.synchronize()
-        ctx0 = eng.length(0)
-        before = ops.launches
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(steps):
-            one()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / steps
+        ms, launches = eng.time_decode_steps(list(range(batch)), toks, warmup, steps, sample=True)
         bytes_step = weight_bytes + batch * (ctx0 + steps / 2.0) * kv_bytes_per_token
-        return ms, ops.launches - before, bytes_step
+        return ms, launches, bytes_step
 
     sampler = ClockSampler()
     sampler.start()
@@ -221,20 +196,20 @@ def main():
             ms_b, _, by = decode_run(b, min(args.steps, 32), 3)
             points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
             points[f"decode_b{b}_hbm_frac"] = round(by / (ms_b * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
-        # a step of 32 decoded tokens beside one 512-token prompt chunk (the small shape's benchmark workload); the same shape
-        # every time, so from its third occurrence on the engine replays it as a graph
+        # a step of 32 decoded tokens beside one 512-token prompt chunk (the small shape's benchmark workload),
+        # launched kernel by kernel every time
         n_dec, chunk = min(32, max_batch), 512
         chunk_ids = ids(chunk)
 
         def mixed_once():
             eng.add_request("chunk")
-            eng.step([StepEntry(i, [chunk_ids[i]], [0]) for i in range(n_dec)] + [StepEntry("chunk", chunk_ids, [chunk - 1])])
+            ms = eng.time_step([StepEntry(i, [chunk_ids[i]], [0]) for i in range(n_dec)] + [StepEntry("chunk", chunk_ids, [chunk - 1])])
             eng.release("chunk")
+            return ms
 
-        for _ in range(4):
+        for _ in range(3):
             mixed_once()
-        points[f"mixed_b{n_dec}_chunk{chunk}_ms"] = round(timed(mixed_once, 5), 3)
-    gemm100.check_errors(dev)
+        points[f"mixed_b{n_dec}_chunk{chunk}_ms"] = round(median([mixed_once() for _ in range(5)]), 3)
     if args.phase == "decode":
         print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": ms_step, "layers": args.layers}))
         return 0
@@ -242,7 +217,6 @@ def main():
     # ---- end to end through the Python entry point ------------------------------------------------------
     for i in range(max_batch):
         eng.release(i)
-    model._seqs = {}
     streams = []
     opts = GenOptions(sampler=SamplerParams.greedy(), max_new_tokens=args.steps + args.warmup + 8, ignore_eog=True)
     for i in range(args.batch):
@@ -250,18 +224,27 @@ def main():
         model.seq_select(seq)
         streams.append(model.stream_begin(ids(PREFIX), opts))
     model.stream_run(streams, args.warmup)
-    torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    model.synchronize()
     t0 = time.perf_counter()
-    s.record()
     done = model.stream_run(streams, args.steps)          # host token ids in, every step's sampled ids out
-    e.record()
-    torch.cuda.synchronize()
+    model.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     assert len(done) == args.steps and all(tok is not None for step in done for _, tok in step)
-    e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / args.steps
-    h2d = eng.last_upload_bytes                                 # the step's packed int32 metadata (ids, positions, tables)
+    h2d = model.engine_info()["upload_bytes"]                   # the step's packed int32 metadata (ids, positions, tables)
     e2e = {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch + 8}
+
+    # ---- the small shape is bound by launches: the same decode with every kernel launched by the host -----------
+    if args.shape == "0.6b" and not args.no_points:
+        for st in streams:
+            st.free()
+        model.kv_cache_init(CONTEXT, max_sequences=3, page_size=16, kv_tokens=2 * (PREFIX + 256), cuda_graphs=False)
+        eng2 = Engine.attach(model)
+        eng2.add_request(0)
+        eng2.step([StepEntry(0, ids(PREFIX), [])])
+        ms_off, launches_off = eng2.time_decode_steps([0], [ids(35)], 3, 32, sample=True)
+        points["decode_b1_graphs_off"] = round(1 / ms_off * 1e3, 1)
+        points["decode_b1_launches_per_step"] = launches_off // 32
 
     value = args.batch / ms_step * 1e3
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
@@ -275,7 +258,7 @@ def main():
                    "layers_of_config": shape["num_hidden_layers"], "hidden": E, "q_heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": D, "intermediate": FF, "vocab": V,
                    "kv_page_tokens": 16, "kv_dtype": "bf16", "l2": f"weights ({weight_bytes / 1e9:.1f} GB) exceed L2 every step",
-                   "cuda_graphs": True, "prefill_tokens": PREFILL_TOKENS},
+                   "cuda_graphs": True, "prefill_tokens": PREFILL_TOKENS, "sampling": "greedy, inside the timed step"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},

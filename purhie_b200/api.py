@@ -134,6 +134,14 @@ class Model:
         """Wait until everything launched so far is done (raises if a kernel reported giving up on a wait)."""
         native.check(native.lib().inference_synchronize(self._h))
 
+    def set_eog_tokens(self, ids: Sequence[int]) -> None:
+        """The end-of-generation token ids (by default those of the model's configuration)."""
+        native.check(native.lib().inference_set_eog_tokens(self._h, native.int32_array(list(ids)), len(ids)))
+
+    def sequence_length_in_cache(self, seq: int) -> int:
+        """Tokens of sequence ``seq`` whose keys are in the cache (the last generated token is fed by the next call)."""
+        return native.lib().engine_request_length(self._h, seq)
+
     def set_seed(self, seed: int) -> None:
         native.lib().inference_set_seed(self._h, int(seed))
 

@@ -309,6 +309,14 @@ API int inference_synchronize(inference_model_t* m) {
     });
 }
 
+API int inference_set_eog_tokens(inference_model_t* m, const int32_t* ids, int n) {
+    return guarded([&] {
+        if (!m || n < 0 || (n > 0 && !ids)) throw Error(kInvalidArg, "a model and n token ids are needed");
+        m->eos_ids.assign(ids, ids + n);
+        return 0;
+    });
+}
+
 API void inference_set_seed(inference_model_t* m, unsigned int seed) { if (m) m->seed = seed; }
 API void inference_set_prefill_batch(inference_model_t* m, int n) { if (m) m->prefill_batch = n < 1 ? 1 : n; }
 

@@ -92,6 +92,9 @@ void inference_kv_cache_free(inference_model_t* model);
 /* Wait until everything the model has launched is done; reports a kernel that gave up on a wait. */
 int inference_synchronize(inference_model_t* model);
 
+/* The end-of-generation token ids (by default config.json's or generation_config.json's eos_token_id). */
+int inference_set_eog_tokens(inference_model_t* model, const int32_t* ids, int n);
+
 void inference_set_seed(inference_model_t* model, unsigned int seed);      /* for inference_generate_ex without params */
 void inference_set_prefill_batch(inference_model_t* model, int n_tokens); /* most tokens per pass of a prefill (default 1024) */
 

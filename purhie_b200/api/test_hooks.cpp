@@ -5,6 +5,7 @@
 // unless it says so.
 #include <algorithm>
 
+#include "../parts/linear.h"
 #include "capi_internal.h"
 
 using namespace qe;
@@ -214,6 +215,26 @@ API const char* qe_sampler_device_mode(sampler_t* s) {
     }
 }
 API int qe_sampler_chain_max_k(void) { return Sampler::kChainMaxK; }
+// The sampler's next uniform number, and the 24-byte record the device's chain kernel takes for its next token
+// (either one draws from the generator, as sampling a token does).
+API double qe_sampler_uniform(sampler_t* s) { return s->s.uniform(); }
+API void qe_sampler_chain_record(sampler_t* s, void* out24) {
+    ChainRecord r = s->s.chain_record();
+    memcpy(out24, &r, sizeof r);
+}
+// The shape the engine picks for the tcgen05 product of M tokens with an [N, K] weight:
+// {"swapped", "block_n", "splits", "pair"}.
+API const char* qe_plan_gemm(int M, int N, int K, int sms, int allow_split, int fused_epilogue) {
+    return guarded_text([&] {
+        GemmPlan p = plan_gemm(M, N, K, sms, allow_split != 0, fused_epilogue != 0);
+        Json j = Json::object();
+        j.set("swapped", p.swapped);
+        j.set("block_n", p.block_n);
+        j.set("splits", p.splits);
+        j.set("pair", p.pair);
+        return j.dump();
+    });
+}
 // `draws` tokens sampled from one row of logits (none accepted); counts[token] is incremented for each.
 API int qe_sampler_histogram(sampler_t* s, const float* logits, int n_vocab, long long draws, long long* counts) {
     return guarded([&] {
@@ -271,6 +292,8 @@ API const char* qe_engine_info(inference_model_t* m) {
         j.set("row_multiple", eng.row_multiple());
         j.set("upload_bytes", (long long)eng.last_upload_bytes());
         j.set("free_slots", c.slots().num_free());
+        j.set("scheduler_steps", m->scheduler->steps);
+        j.set("preemptions", m->scheduler->preemptions);
         return j.dump();
     });
 }
@@ -287,6 +310,83 @@ API int qe_engine_set_error_word(inference_model_t* m, int which, int code) {
         return 0;
     });
 }
+// ---- timing on the device, for the benchmark ---------------------------------------------------------------------------
+// `warmup + steps` decode steps of n requests (live, each with its prefix in the cache): step k feeds request i the
+// token tokens[i * (warmup + steps) + k] from the host, and, with `sample`, every step's logits go through the greedy
+// sampling kernel with the ids copied to the host, nobody waiting for them.  The last `steps` steps are bracketed
+// by CUDA events on the engine's stream; *ms_per_step is their mean, *launches the launcher calls they made.
+API int qe_time_decode_steps(inference_model_t* m, const long long* requests, int n, const int32_t* tokens, int warmup, int steps,
+                             int sample, double* ms_per_step, long long* launches) {
+    return guarded([&] {
+        Engine& eng = need_engine(m);
+        const int total = warmup + steps;
+        std::vector<Sampler> greedy((size_t)n, Sampler(SamplerParams::greedy()));
+        std::vector<Sampler*> samplers;
+        for (Sampler& s : greedy) samplers.push_back(&s);
+        static const int32_t kFirst[1] = {0};
+        cudaEvent_t t0, t1;
+        QE_CUDA(cudaEventCreate(&t0));
+        QE_CUDA(cudaEventCreate(&t1));
+        long long before = 0;
+        for (int k = 0; k < total; k++) {
+            if (k == warmup) {
+                QE_CUDA(cudaStreamSynchronize(eng.stream()));
+                before = g_launches;
+                QE_CUDA(cudaEventRecord(t0, eng.stream()));
+            }
+            std::vector<StepEntry> entries((size_t)n);
+            for (int i = 0; i < n; i++) {
+                entries[i].request = requests[i];
+                entries[i].tokens = tokens + (size_t)i * total + k;
+                entries[i].n_tokens = 1;
+                entries[i].want = kFirst;
+                entries[i].n_want = 1;
+            }
+            Tensor logits = eng.step(entries);
+            if (sample) eng.sample_async(logits, samplers);
+        }
+        QE_CUDA(cudaEventRecord(t1, eng.stream()));
+        QE_CUDA(cudaEventSynchronize(t1));
+        float ms = 0;
+        QE_CUDA(cudaEventElapsedTime(&ms, t0, t1));
+        cudaEventDestroy(t0);
+        cudaEventDestroy(t1);
+        eng.check_kernel_errors();
+        if (ms_per_step) *ms_per_step = (double)ms / steps;
+        if (launches) *launches = g_launches - before;
+        return 0;
+    });
+}
+// One batch through the step function, bracketed by CUDA events on the engine's stream (the logits stay on the
+// device).  *ms: the device time of the step.
+API int qe_time_step(inference_model_t* m, const engine_step_batch* batch, double* ms) {
+    return guarded([&] {
+        Engine& eng = need_engine(m);
+        std::vector<StepEntry> entries((size_t)batch->n_entries);
+        for (int i = 0; i < batch->n_entries; i++) {
+            const engine_step_entry& e = batch->entries[i];
+            entries[i].request = e.request;
+            entries[i].tokens = e.tokens; entries[i].n_tokens = e.n_tokens;
+            entries[i].want = e.want; entries[i].n_want = e.n_want;
+        }
+        cudaEvent_t t0, t1;
+        QE_CUDA(cudaEventCreate(&t0));
+        QE_CUDA(cudaEventCreate(&t1));
+        QE_CUDA(cudaStreamSynchronize(eng.stream()));
+        QE_CUDA(cudaEventRecord(t0, eng.stream()));
+        eng.step(entries);
+        QE_CUDA(cudaEventRecord(t1, eng.stream()));
+        QE_CUDA(cudaEventSynchronize(t1));
+        float f = 0;
+        QE_CUDA(cudaEventElapsedTime(&f, t0, t1));
+        cudaEventDestroy(t0);
+        cudaEventDestroy(t1);
+        eng.check_kernel_errors();
+        if (ms) *ms = f;
+        return 0;
+    });
+}
+
 API long long qe_launches(void) { return g_launches; }
 API void qe_set_library_dir(const char* dir) { set_library_dir(dir ? dir : ""); }
 

@@ -59,7 +59,7 @@ LIBRARIES: Dict[str, dict] = {
                  "../cache/cache.h", "../sampling/sampler.h", "../engine/engine.h", "../engine/scheduler.h",
                  "../api/inference.h", "../api/capi_internal.h"],
         "flags": ["-Xcompiler", "-ffp-contract=off"],
-        "link": ["-ldl"],
+        "link": ["-ldl", "-lpthread"],
         "file_name": "libqengine.so",
     },
     # decode attention with its scratch in a fixed device array, for callers that cannot allocate

@@ -1,8 +1,10 @@
 """Python faces of the CUDA kernels: torch tensors in, launches on the current stream.
 
-Every function checks what the kernel cannot check cheaply (device, dtype, contiguity, shapes) and
-raises :class:`KernelError` with the library's message when a launcher refuses.  Nothing here computes on
-the host, and nothing falls back to a library implementation: a missing library is an error.
+These serve the kernels' own tests and measurements (each kernel beside a plain reference, at sizes of the test's
+choosing); the engine launches the same exported functions from its C++ parts.  Every function checks what the
+kernel cannot check cheaply (device, dtype, contiguity, shapes) and raises :class:`KernelError` with the library's
+message when a launcher refuses.  Nothing here computes on the host, and nothing falls back to a library
+implementation: a missing library is an error.
 """
 from __future__ import annotations
 
@@ -17,8 +19,29 @@ from .build import load_library
 F32, BF16 = 0, 1
 
 
-class KernelError(RuntimeError):
-    pass
+from ..native import KernelError  # noqa: E402  (the library's error kind, shared with the engine's face)
+
+
+class Workspace:
+    """Scratch tensors by name for the faces that need some (split-key partial results), reused and grown on demand;
+    ``frozen`` turns growth into an error, as under a captured graph."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs = {}
+        self.frozen = False
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        buf = self._bufs.get((name, dtype))
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[(name, dtype)] = buf
+        return buf[:n].view(*shape)
 
 
 def _code(dtype: torch.dtype) -> int:

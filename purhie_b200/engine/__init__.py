@@ -40,11 +40,18 @@ class Engine:
 
     def __init__(self, handle, *, page_size: int = 16, max_tokens: int = 4096, max_requests: int = 4, num_pages=None,
                  poison_cache: bool = False, cuda_graphs: bool = True, step_options: Optional[dict] = None,
-                 n_ctx: int = 0, engine_options: Optional[dict] = None):
+                 n_ctx: int = 0, engine_options: Optional[dict] = None, attach: bool = False):
         L = native.lib()
         self._handle = handle
+        self._owns = not attach
         self._ids: Dict[object, int] = {}
         self._next_id = 1 << 20                       # clear of the sequence numbers of the C API
+        self.last_stats = StepStats()
+        if attach:                                    # a model whose cache somebody else made (purhie_b200.api.Model)
+            self.vocab_size = L.inference_vocab_size(handle)
+            self.hidden_size = L.inference_hidden_size(handle)
+            self.page_size, self.max_requests = page_size, L.inference_batch_size(handle)
+            return
         native.ensure_libraries_for(handle)
         opts = dict(engine_options or {})
         opts.update({"poison_cache": poison_cache, "cuda_graphs": cuda_graphs})
@@ -97,10 +104,16 @@ class Engine:
         the same seed."""
         return cls(cls.random_handle(config, seed, dtype, std, scale_low, scale_high, options), **kw)
 
+    @classmethod
+    def attach(cls, model) -> "Engine":
+        """The step function of a :class:`purhie_b200.api.Model` whose cache is made already: the same engine its
+        generation uses, with requests of its own beside the model's sequences."""
+        return cls(model.handle, attach=True)
+
     def close(self) -> None:
-        if self._handle:
+        if self._handle and self._owns:
             native.lib().inference_free_model(self._handle)
-            self._handle = None
+        self._handle = None
 
     def __del__(self):
         try:
@@ -144,13 +157,24 @@ class Engine:
         entries = list(entries)
         if not entries:
             return None
+        batch, keep, wanted = self._batch(entries)
+        out = native.StepOutputC()
+        logits = np.empty((max(wanted, 1), self.vocab_size), dtype=np.float32)
+        out.logits = logits.ctypes.data_as(POINTER(c_float))
+        out.logits_capacity = logits.size
+        native.check(native.lib().engine_step(self._handle, ctypes.byref(batch), ctypes.byref(out)))
+        self.last_stats = StepStats(out.tokens, out.prompt_rows, out.decode_rows, out.n_rows, bool(out.replayed_graph))
+        return logits[:out.n_rows] if out.n_rows else None
+
+    def _batch(self, entries):
+        """The C batch for ``entries`` (and the arrays it points into, which the caller keeps alive)."""
         seen = set()
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} is in the batch twice")
             seen.add(e.request_id)
         arr = (native.StepEntryC * len(entries))()
-        keep = []
+        keep = [arr]
         wanted = 0
         for i, e in enumerate(entries):
             toks = np.ascontiguousarray(np.asarray(e.tokens, dtype=np.int64))
@@ -165,14 +189,28 @@ class Engine:
             arr[i].want = want.ctypes.data_as(POINTER(c_int32))
             arr[i].n_want = int(want.size)
             wanted += int(want.size)
-        out = native.StepOutputC()
-        logits = np.empty((max(wanted, 1), self.vocab_size), dtype=np.float32)
-        out.logits = logits.ctypes.data_as(POINTER(c_float))
-        out.logits_capacity = logits.size
-        batch = native.StepBatchC(arr, len(entries))
-        native.check(native.lib().engine_step(self._handle, ctypes.byref(batch), ctypes.byref(out)))
-        self.last_stats = StepStats(out.tokens, out.prompt_rows, out.decode_rows, out.n_rows, bool(out.replayed_graph))
-        return logits[:out.n_rows] if out.n_rows else None
+        return native.StepBatchC(arr, len(entries)), keep, wanted
+
+    # ---- timing on the device (the benchmark's) ------------------------------------------------------------------
+    def time_step(self, entries: Sequence[StepEntry]) -> float:
+        """Run one batch between two CUDA events on the engine's stream; returns its milliseconds.  The logits stay
+        on the device."""
+        batch, keep, _ = self._batch(list(entries))
+        ms = ctypes.c_double(0.0)
+        native.check(native.lib().qe_time_step(self._handle, ctypes.byref(batch), ctypes.byref(ms)))
+        return ms.value
+
+    def time_decode_steps(self, request_ids: Sequence, tokens, warmup: int, steps: int, sample: bool = True):
+        """``warmup + steps`` decode steps of the given live requests: ``tokens[i][k]`` is what request i is fed in
+        step k (host ids in every step); with ``sample`` every step's logits go through the greedy sampling kernel and
+        the ids are copied to the host.  Returns (milliseconds per step over the last ``steps``, launcher calls)."""
+        n = len(request_ids)
+        ids = (ctypes.c_longlong * n)(*[self._id(r) for r in request_ids])
+        toks = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(n, warmup + steps))
+        ms, launches = ctypes.c_double(0.0), ctypes.c_longlong(0)
+        native.check(native.lib().qe_time_decode_steps(self._handle, ids, n, toks.ctypes.data_as(POINTER(c_int32)), warmup, steps,
+                                                       int(sample), ctypes.byref(ms), ctypes.byref(launches)))
+        return ms.value, launches.value
 
     # ---- a look inside ----------------------------------------------------------------------------------------
     def info(self) -> dict:

@@ -136,6 +136,7 @@ _SIGNATURES = {
     "inference_kv_cache_init_ex": (c_int, [_P, c_int, c_int, c_int, c_longlong, c_char_p]),
     "inference_kv_cache_free": (None, [_P]),
     "inference_synchronize": (c_int, [_P]),
+    "inference_set_eog_tokens": (c_int, [_P, POINTER(c_int32), c_int]),
     "inference_set_seed": (None, [_P, c_uint]),
     "inference_set_prefill_batch": (None, [_P, c_int]),
     "inference_reset": (None, [_P]),
@@ -192,12 +193,18 @@ _SIGNATURES = {
     "qe_random_tensor": (c_int, [c_char_p, c_char_p, c_longlong, c_uint64, c_double, c_double, c_double, POINTER(c_float)]),
     "qe_sampler_device_mode": (c_char_p, [_P]),
     "qe_sampler_chain_max_k": (c_int, []),
+    "qe_sampler_uniform": (c_double, [_P]),
+    "qe_sampler_chain_record": (None, [_P, c_void_p]),
+    "qe_plan_gemm": (c_char_p, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "qe_sampler_histogram": (c_int, [_P, POINTER(c_float), c_int, c_longlong, POINTER(c_longlong)]),
     "qe_model_required_libraries": (c_char_p, [_P]),
     "qe_engine_info": (c_char_p, [_P]),
     "qe_engine_cache_check": (c_int, [_P]),
     "qe_engine_set_error_word": (c_int, [_P, c_int, c_int]),
     "qe_engine_set_layer_dump": (c_int, [_P, LAYER_DUMP_CB, c_void_p]),
+    "qe_time_step": (c_int, [_P, POINTER(StepBatchC), POINTER(c_double)]),
+    "qe_time_decode_steps": (c_int, [_P, POINTER(c_longlong), c_int, POINTER(c_int32), c_int, c_int, c_int, POINTER(c_double),
+                                     POINTER(c_longlong)]),
     "qe_launches": (c_longlong, []),
     "qe_set_library_dir": (None, [c_char_p]),
 }

@@ -70,6 +70,17 @@ class Sampler:
         result as the chain on the host, else None (penalties, top-p or min-p without top-k)."""
         return native.lib().qe_sampler_device_mode(self._h).decode() or None
 
+    def uniform(self) -> float:
+        """The generator's next uniform number in [0, 1) (what sampling one token draws)."""
+        return native.lib().qe_sampler_uniform(self._h)
+
+    def chain_record(self) -> bytes:
+        """The 24-byte record (uniform, top_p, log(min_p) or -inf, temperature, top_k) the device's chain kernel takes
+        for this sampler's next token; draws the token's uniform number."""
+        buf = ctypes.create_string_buffer(24)
+        native.lib().qe_sampler_chain_record(self._h, buf)
+        return buf.raw
+
     @staticmethod
     def chain_max_k() -> int:
         return native.lib().qe_sampler_chain_max_k()

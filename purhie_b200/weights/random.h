@@ -54,8 +54,11 @@ QE_HD uint64_t word(uint64_t key, uint64_t i, uint64_t k) { return mix64(key + (
 
 // ln(n * 2^-53) for an integer n in [1, 2^53].
 QE_HD double log_unit(uint64_t n) {
-    int b = 63;
-    while (!((n >> b) & 1)) b--;                            // highest set bit
+#if defined(__CUDA_ARCH__)
+    int b = 63 - __clzll((long long)n);                     // highest set bit
+#else
+    int b = 63 - __builtin_clzll(n);
+#endif
     double m = mul((double)n, 1.0 / (double)(1ULL << b));   // in [1, 2), exact
     if (m > 1.4142135623730951) { m = mul(m, 0.5); b++; }
     const double s = div(add(m, -1.0), add(m, 1.0));        // |s| <= 0.1716; ln m = 2 atanh s

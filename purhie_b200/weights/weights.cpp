@@ -6,6 +6,7 @@
 #include <cerrno>
 #include <fstream>
 #include <set>
+#include <thread>
 
 #include "../parts/model.h"
 #include "random.h"
@@ -195,11 +196,21 @@ void write_random_model(const std::string& model_dir, const ModelConfig& config,
             size_t n = 1;
             for (auto s : spec.shape) n *= (size_t)s;
             const uint64_t key = rnd::tensor_key(init.seed, spec.name.c_str());
-            for (size_t i = 0; i < n; i++) {
-                const float v = rnd::random_value(key, i, kind, a, b);
-                if (dt == DType::F32) memcpy(dst + 4 * i, &v, 4);
-                else { uint16_t h = f32_to_bf16(v); memcpy(dst + 2 * i, &h, 2); }
-            }
+            // every element is a function of its index: slices of a large tensor are filled by threads side by side
+            auto fill_range = [=](size_t first, size_t last) {
+                for (size_t i = first; i < last; i++) {
+                    const float v = rnd::random_value(key, i, kind, a, b);
+                    if (dt == DType::F32) memcpy(dst + 4 * i, &v, 4);
+                    else { uint16_t h = f32_to_bf16(v); memcpy(dst + 2 * i, &h, 2); }
+                }
+            };
+            const size_t workers = n < (1u << 16) ? 1 : std::max(1u, std::min(32u, std::thread::hardware_concurrency()));
+            if (workers == 1) { fill_range(0, n); return; }
+            std::vector<std::thread> pool;
+            const size_t per = (n + workers - 1) / workers;
+            for (size_t w = 0; w < workers; w++)
+                if (w * per < n) pool.emplace_back(fill_range, w * per, std::min(n, (w + 1) * per));
+            for (std::thread& t : pool) t.join();
         };
         out.push_back(std::move(t));
     }

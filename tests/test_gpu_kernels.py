@@ -137,13 +137,20 @@ def test_gemm_tcgen05_pair_with_k_in_parts(M, N, K, splits):
 
 
 def test_plan_for_many_tokens_keeps_a_fused_epilogue_whole_and_fills_the_device():
-    from purhie_b200.csrc.gemm100 import plan_many
-    assert plan_many(2048, 24576, 4096, 148, True, fused_epilogue=True) == (True, 1)
-    assert plan_many(512, 24576, 4096, 148, True, fused_epilogue=True)[1] == 1
-    pair, splits = plan_many(512, 4096, 12288, 148, True)            # 32 tiles of 256 x 256 on 74 pairs: K is cut
+    from purhie_b200 import native
+
+    def plan(M, N, K, allow_split, fused=False):
+        p = native.answer(native.lib().qe_plan_gemm(M, N, K, 148, int(allow_split), int(fused)))
+        return p["pair"], p["splits"], p["swapped"]
+
+    assert plan(2048, 24576, 4096, True, fused=True)[:2] == (True, 1)
+    assert plan(512, 24576, 4096, True, fused=True)[1] == 1
+    pair, splits, _ = plan(512, 4096, 12288, True)                   # 32 tiles of 256 x 256 on 74 pairs: K is cut
     assert splits > 1
-    assert plan_many(512, 4096, 12288, 148, False)[1] == 1
-    assert plan_many(128, 4096, 4096, 148, True)[0] is False         # one tile high: no second CTA to pair with
+    assert plan(512, 4096, 12288, False)[1] == 1
+    assert plan(128, 4096, 4096, True)[0] is False                   # one tile high: no second CTA to pair with
+    few = plan(8, 4096, 12288, True)                                 # few tokens: weights on the wide side, K in parts
+    assert few[2] is True and few[1] > 1 and plan(8, 4096, 12288, False)[1] == 1
 
 
 def test_gemm_tcgen05_pair_equals_one_cta_kernel():
@@ -357,7 +364,7 @@ def run_generic(case, HQ, HKV, D, page_size, window, scale, out_dtype):
 
 def run_flash(case, HQ, HKV, D, page_size, window, scale, splits=None, bulk=True, max_ctas=0, tc5=True, tile_splits=1):
     from purhie_b200.csrc import flash
-    from purhie_b200.parts.context import Workspace
+    from purhie_b200.csrc.ops import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
     tile_seg, tile_first, dec_rows, start = [], [], [], 0
     for s, (ctx, ql) in enumerate(case["segs"]):
@@ -605,7 +612,7 @@ def test_sample_chain_equals_the_host_chain(V):
             a, b = Sampler(prm), Sampler(prm)
             assert b.device_mode() == "chain"
             host.append(a.sample(logits[r].numpy()))
-            rec[r] = b.chain_record()
+            rec[r:r + 1] = np.frombuffer(b.chain_record(), dtype=ops.CHAIN_ROW)
         out = torch.empty(R, dtype=torch.int32, device=DEV)
         ops.sample_chain(dev, torch.from_numpy(rec.view(np.uint8).reshape(R, 24)).to(DEV), out)
         device = out.cpu().tolist()
@@ -622,7 +629,7 @@ def test_decode_attention_sees_the_key_written_by_the_kernel_in_front(ctx, split
     is written, so a request issued too early finds NaN (seen in a handful of rows per run with the check on the
     split instead of on the block)."""
     from purhie_b200.csrc import flash, ops
-    from purhie_b200.parts.context import Workspace
+    from purhie_b200.csrc.ops import Workspace
     HQ, HKV, D, ps, R = 32, 8, 128, 16, 2048
     scale = 1.0 / math.sqrt(D)
     pages_per = -(-ctx // ps)

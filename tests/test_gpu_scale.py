@@ -1,12 +1,13 @@
-"""The bfloat16 engine against the float32 engine at real layer sizes (GPU).
+"""The engine at real layer sizes (GPU): float32 against the plain implementation, bfloat16 against float32.
 
 The tiny configurations of the other tests leave paths untouched that only real sizes reach: a decode row whose
-context is cut into more splits than it has blocks to fill, products on pairs of CTAs, K in parts, attention
-tiles shared by several CTAs.  Two layers of an 8B-class shape (hidden 4096, 32 query heads over 8 kv heads of
-128, feed-forward 12288), of a 0.6B-class shape (hidden 1024 under a query width of 2048, tied embeddings) and of a
-32B-class shape (hidden 5120, groups of eight query heads, feed-forward 25600) with random weights: whatever way the
-tokens are fed, the bfloat16 engine must stay as close to the float32 engine as it is for a whole prompt.
+context is cut into more splits than it has blocks to fill, products on pairs of CTAs, K in parts, attention tiles
+shared by several CTAs, sums over 12,288 terms.  Two layers of an 8B-class shape (hidden 4096, 32 query heads over 8
+kv heads of 128, feed-forward 12288), of a 0.6B-class shape (hidden 1024 under a query width of 2048, tied
+embeddings) and of a 32B-class shape (hidden 5120, groups of eight query heads, feed-forward 25600) with random
+weights and the vocabulary cut to 32,000.
 """
+import numpy as np
 import pytest
 import torch
 
@@ -21,30 +22,30 @@ SHAPES = {"8b": SHAPE,
 
 
 def rel(a, b):
-    return float((a.double() - b.double()).norm() / b.double().norm())
+    a, b = torch.as_tensor(a).double(), torch.as_tensor(b).double()
+    return float((a - b).norm() / b.norm())
+
+
+def ids(n, seed, vocab=32000):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
 
 
 @pytest.mark.parametrize("shape", sorted(SHAPES))
 def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt(shape):
-    from purhie_b200.api import load_model_random
-    from purhie_b200.config import Qwen3Config
     from purhie_b200.engine import Engine, StepEntry
-    cfg = Qwen3Config.from_dict(SHAPES[shape])
-    g = torch.Generator().manual_seed(11)
-    toks = torch.randint(0, cfg.vocab_size, (2700,), generator=g).tolist()
-    others = [torch.randint(0, cfg.vocab_size, (n + 24,), generator=g).tolist() for n in (17, 300, 1000, 2047, 64, 129, 700)]
+    toks = ids(2700, 11)
+    others = [ids(n + 24, 20 + i) for i, n in enumerate((17, 300, 1000, 2047, 64, 129, 700))]
     out = {}
     for dtype in ("float32", "bfloat16"):
-        m = load_model_random(cfg, 7, dtype, "cuda:0")
-        eng = Engine(m._decoder, cfg, page_size=16, max_tokens=16384, max_requests=8)
+        eng = Engine.from_random(SHAPES[shape], 7, dtype=dtype, page_size=16, max_tokens=16384, max_requests=8)
         res = {}
         eng.add_request("w")
-        res["whole"] = eng.step([StepEntry("w", toks[:2524], list(range(2499, 2524)))]).clone()      # from the prompt's last place on
+        res["whole"] = eng.step([StepEntry("w", toks[:2524], list(range(2499, 2524)))])      # from the prompt's last place on
         eng.release("w")
         # one request decoding alone at 2,500 tokens: its context is cut into more splits than it has blocks for
         eng.add_request("d")
         eng.step([StepEntry("d", toks[:2500], [])])
-        res["decode"] = torch.cat([eng.step([StepEntry("d", [toks[2500 + k]], [0])]).clone() for k in range(24)])
+        res["decode"] = np.concatenate([eng.step([StepEntry("d", [toks[2500 + k]], [0])]) for k in range(24)])
         # ... then beside seven others of other lengths, and beside a prompt that comes in chunks
         for i, o in enumerate(others):
             eng.add_request(i)
@@ -52,22 +53,21 @@ def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt(shape):
         rows = []
         for k in range(24):
             ent = [StepEntry("d", [toks[2524 + k]], [0])] + [StepEntry(i, [o[len(o) - 24 + k]], []) for i, o in enumerate(others)]
-            rows.append(eng.step(ent).clone())
-        res["batch"] = torch.cat(rows)
+            rows.append(eng.step(ent))
+        res["batch"] = np.concatenate(rows)
         for i in range(len(others)):
             eng.release(i)
         # a short portion late in the context: one attention tile that looks back over 2,600 keys, shared by several CTAs
-        res["late"] = eng.step([StepEntry("d", toks[2548:2600], [0, 25, 51])]).clone()
+        res["late"] = eng.step([StepEntry("d", toks[2548:2600], [0, 25, 51])])
         eng.add_request("c")
         for s in range(0, 2500, 500):
             lg = eng.step([StepEntry("c", toks[s:s + 500], [499] if s + 500 >= 2500 else [])])
-        res["chunks"] = lg.clone()
+        res["chunks"] = lg
         out[dtype] = res
-        del eng, m
-        torch.cuda.empty_cache()
+        eng.close()
     f32, b16 = out["float32"], out["bfloat16"]
-    assert torch.equal(f32["whole"][1:], f32["decode"])               # float32: the same bits however it is fed
-    assert torch.equal(f32["whole"][:1], f32["chunks"])
+    assert np.array_equal(f32["whole"][1:], f32["decode"])               # float32: the same bits however it is fed
+    assert np.array_equal(f32["whole"][:1], f32["chunks"])
     whole = rel(b16["whole"], f32["whole"])
     assert whole < 3e-2
     for name, want in (("decode", f32["whole"][1:]), ("chunks", f32["whole"][:1])):
@@ -78,4 +78,70 @@ def test_every_way_of_feeding_is_as_close_to_float32_as_a_whole_prompt(shape):
     for name in ("batch", "late"):
         err = rel(b16[name], f32[name])
         assert err < 1.5 * whole + 2e-3, f"{name}: {err:.3e} against {whole:.3e}"
-        assert not torch.isnan(b16[name]).any()
+        assert not np.isnan(b16[name]).any()
+
+
+@pytest.mark.parametrize("n_decode,portion", [(8, 512), (32, 512), (32, 480)])
+def test_a_prompt_portion_beside_decode_rows_at_real_layer_sizes(n_decode, portion):
+    """One step with decode rows beside a prompt portion at the 8B-class layer shape: 520 or 544 rows through the
+    products on CTA pairs, the portion through the tcgen05 attention and the decode rows through the split-key
+    attention, all in one pass.  float32 gives the bits of the same tokens fed in steps of their own; bfloat16 stays
+    as close to float32 as it is for a whole prompt."""
+    from purhie_b200.engine import Engine, StepEntry
+    prompt = ids(1024 + portion, 5)
+    decoders = [ids(40 + 37 * i, 100 + i) for i in range(n_decode)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        for mode in ("mixed", "apart"):
+            eng = Engine.from_random(SHAPES["8b"], 7, dtype=dtype, page_size=16, max_tokens=65536, max_requests=n_decode + 1)
+            eng.add_request("p")
+            eng.step([StepEntry("p", prompt[:1024], [])])
+            for i, d in enumerate(decoders):
+                eng.add_request(i)
+                eng.step([StepEntry(i, d[:-1], [])])
+            dec = [StepEntry(i, d[-1:], [0]) for i, d in enumerate(decoders)]
+            por = StepEntry("p", prompt[1024:], [0, portion // 2, portion - 1])
+            if mode == "mixed":
+                got[dtype, mode] = eng.step(dec + [por])
+            else:
+                got[dtype, mode] = np.concatenate([eng.step(dec), eng.step([por])])
+            eng.close()
+    assert np.array_equal(got["float32", "mixed"], got["float32", "apart"])
+    base = rel(got["bfloat16", "apart"], got["float32", "apart"])
+    assert base < 3e-2
+    err = rel(got["bfloat16", "mixed"], got["float32", "mixed"])
+    assert err < 1.5 * base + 2e-3 and not np.isnan(got["bfloat16", "mixed"]).any()
+
+
+def test_float32_at_the_8b_layer_shape_agrees_with_the_plain_implementation(tmp_path):
+    """Two layers at hidden 4096, 32 query heads over 8 kv heads of 128 and feed-forward 12288: the float32 engine
+    against the plain implementation (float64, whole sequences) to 1e-4 of the largest logit with the same argmax,
+    for a whole prompt, decoding and a chunked feed; the bfloat16 engine against the same plain logits to 3e-2."""
+    from helpers import same_top1_or_near_tie
+    from plain import qwen3_plain as P
+    from purhie_b200.engine import Engine, StepEntry
+    from purhie_b200.weights import write_random_model
+    toks = ids(104, 3)
+    folders = {}
+    for dtype in ("float32", "bfloat16"):
+        folders[dtype] = str(tmp_path / dtype)
+        write_random_model(folders[dtype], SHAPES["8b"], 2, 0.02, 1.0, 1.0, dtype)
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 3e-2)):
+        pc, pw = P.read_model(folders[dtype])
+        ref = P.forward(pc, pw, toks)
+        eng = Engine.from_folder(folders[dtype], dtype=dtype, page_size=16, max_tokens=1024, max_requests=3)
+        eng.add_request("whole"); eng.add_request("decode"); eng.add_request("chunks")
+        whole = eng.step([StepEntry("whole", toks, list(range(len(toks))))])
+        head = eng.step([StepEntry("decode", toks[:96], list(range(96)))])
+        tail = [eng.step([StepEntry("decode", toks[96 + k:97 + k], [0])]) for k in range(8)]
+        chunks = [eng.step([StepEntry("chunks", toks[s:s + 40], list(range(len(toks[s:s + 40]))))]) for s in range(0, 104, 40)]
+        eng.close()
+        for name, got in (("whole", whole), ("decode", np.concatenate([head] + tail)), ("chunks", np.concatenate(chunks))):
+            got = torch.from_numpy(got.copy())
+            err = float((got.double() - ref).abs().max() / ref.abs().max())
+            assert err < tol, f"{dtype}/{name}: {err:.3e}"
+            if dtype == "float32":
+                assert torch.equal(got.argmax(-1), ref.argmax(-1)), f"{dtype}/{name}: argmax"
+                assert np.array_equal(got.numpy(), whole), f"{name}: float32 is not bit-equal across the cuts"
+            else:
+                assert not same_top1_or_near_tie(got, ref, tol), f"{dtype}/{name}: argmax differs away from a tie"

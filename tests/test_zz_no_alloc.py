@@ -47,7 +47,7 @@ def _call_static(fn, case, HQ, HKV, D, page_size, splits, window, scale):
 
 def _call_ordinary(case, HQ, HKV, D, page_size, splits, window, scale):
     from purhie_b200.csrc import flash
-    from purhie_b200.parts.context import Workspace
+    from purhie_b200.csrc.ops import Workspace
     out = torch.full((case["T"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
     flash.decode(case["q"], case["k_base"], case["v_base"], case["page_stride"], page_size, case["table"], None, case["T"],
                  case["row_seg"], case["positions"], out, Workspace(DEV), num_heads=HQ, num_kv_heads=HKV, head_dim=D,
