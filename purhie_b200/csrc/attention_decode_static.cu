@@ -2,8 +2,12 @@
 // caller-allocated memory.  See attention_decode_static.h for who needs it and what it costs.
 //
 // The kernels are the ones of attention_flash.cu, compiled into this library a second time by including that
-// file; only the source of the scratch differs.
+// file; only the source of the scratch differs.  That file's own entry points stay inside this library (hidden),
+// so that a host which links both libraries meets every symbol once.
+#define PH_EXPORT extern "C" __attribute__((visibility("hidden")))
 #include "attention_flash.cu"
+#undef PH_EXPORT
+#define PH_EXPORT extern "C" __attribute__((visibility("default")))
 
 #include "attention_decode_static.h"
 
@@ -44,9 +48,10 @@ PH_EXPORT int ph_attention_decode_static(const void* q, const void* k_base, cons
                                          int window, float scale, cudaStream_t stream) {
     if (n_rows < 0 || HQ < 1 || splits < 1 || D < 1)
         return ph::fail(PH_ERR_ARG, "attention_decode_static: bad arguments (rows %d, HQ %d, D %d, splits %d)", n_rows, HQ, D, splits);
-    // part_o [rows][HQ][splits][D] followed by part_ml [rows][HQ][splits][2]
+    // part_o [rows][HQ][splits][D] followed by part_ml [rows][HQ][splits][2]; with the keys in one piece the
+    // kernel writes its result directly and touches no scratch, so nothing is needed and nothing is refused
     const unsigned long long slots = (unsigned long long)n_rows * HQ * splits;
-    const unsigned long long need = slots * (unsigned long long)(D + 2) * sizeof(float);
+    const unsigned long long need = splits > 1 ? slots * (unsigned long long)(D + 2) * sizeof(float) : 0;
     if (need > PH_DECODE_STATIC_SCRATCH_BYTES)
         return ph::fail(PH_ERR_UNSUPPORTED,
                         "attention_decode_static: %d rows x %d heads x %d splits x head size %d need %llu bytes of scratch, "

@@ -14,8 +14,11 @@
 // The price and the rules:
 //   * The array is PH_DECODE_STATIC_SCRATCH_BYTES (16 MiB) of device memory on EVERY GPU that loads the
 //     library, held until the process exits, whether or not the entry point is ever called.
-//   * A call needs n_rows * HQ * splits * (D + 2) floats of it; a call that needs more is refused with
-//     PH_ERR_UNSUPPORTED and a message that names both numbers (nothing is launched).
+//   * A call with splits > 1 needs n_rows * HQ * splits * (D + 2) floats of it; a call that needs more is refused
+//     with PH_ERR_UNSUPPORTED and a message that names both numbers (nothing is launched).  With splits == 1 the
+//     kernel writes its result directly, no scratch is touched and no size is refused.
+//   * The library exports these two symbols only; the kernels it shares with libpurhie_flash are private copies, so
+//     a host may link both libraries.
 //   * All calls share the array and it keeps what the last call left there.  Nothing in it has to start at
 //     zero: every slot a call reads was written by that same call first.  Two calls whose kernels may run at
 //     the same time on one GPU (different streams, different threads) race on the array; issue them on one

@@ -251,13 +251,17 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
 }
 
-// Raise a kernel's dynamic shared-memory limit, once per kernel (TAG tells kernels of one signature apart).
+// Raise a kernel's dynamic shared-memory limit, once per kernel and device (TAG tells kernels of one signature
+// apart; the attribute belongs to the kernel as loaded on one device).
 template <int TAG, typename K> int set_smem(K kernel, int bytes) {
-    static bool done = false;
-    if (done || bytes <= 48 * 1024) return PH_OK;
+    static bool done[64] = {false};
+    if (bytes <= 48 * 1024) return PH_OK;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (done[dev]) return PH_OK;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
         return fail(PH_ERR_LAUNCH, "attention_flash: cannot reserve %d bytes of shared memory", bytes);
-    done = true;
+    done[dev] = true;
     return PH_OK;
 }
 

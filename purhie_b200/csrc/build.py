@@ -53,7 +53,7 @@ LIBRARIES: Dict[str, dict] = {
                     "../parts/attention.cpp", "../parts/feed_forward.cpp", "../parts/embedding.cpp", "../parts/block.cpp",
                     "../parts/model.cpp", "../cache/cache.cpp", "../sampling/sampler.cpp", "../engine/engine.cpp",
                     "../engine/scheduler.cpp", "../api/capi.cpp", "../api/capi_generate.cpp", "../api/test_hooks.cpp",
-                    "../api/test_hooks_host.cpp"],
+                    "../api/test_hooks_host.cpp", "../api/test_hooks_parts.cpp"],
         "deps": ["../host/common.h", "../host/json.h", "../host/device.h", "../config/config.h", "../weights/safetensors.h",
                  "../weights/weights.h", "../weights/random.h", "../parts/parts.h", "../parts/linear.h", "../parts/model.h",
                  "../cache/cache.h", "../sampling/sampler.h", "../engine/engine.h", "../engine/scheduler.h",
@@ -205,3 +205,21 @@ def load_library(name: str) -> ctypes.CDLL:
 
 def build_all(verbose: bool = True) -> List[str]:
     return [build_library(n, verbose) for n in LIBRARIES]
+
+
+def build_plugin(source: str, out_dir: str, verbose: bool = True) -> str:
+    """Compile ``source`` (a .cu or .cpp file of parts that includes ``purhie_b200/parts/parts.h``) for sm_100a into a
+    shared object in ``out_dir``, linked against the host library; returns its path.  Open it with
+    :func:`purhie_b200.parts.load_plugin`: its ``qe_plugin_init`` registers what it brings."""
+    host = build_library("qengine", verbose)
+    nvcc = find_nvcc()
+    os.makedirs(out_dir, exist_ok=True)
+    so = os.path.join(out_dir, "lib" + os.path.splitext(os.path.basename(source))[0] + ".so")
+    root = os.path.dirname(os.path.dirname(CSRC))                    # the folder that holds the purhie_b200 package
+    lib_dir = os.path.dirname(host)
+    cmd = [nvcc] + ARCH_FLAGS + ["-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", root, "-I", CSRC, source, "-o", so,
+                                 "-L", lib_dir, "-lqengine", "-Xlinker", "-rpath", "-Xlinker", lib_dir]
+    if verbose:
+        _log(f"compiling the plugin {os.path.basename(source)} into {out_dir}")
+    _run_with_heartbeat([cmd], os.path.basename(source))
+    return so

@@ -20,7 +20,11 @@
 #define PH_F32 0
 #define PH_BF16 1
 
+// A library that compiles another library's source into itself defines PH_EXPORT first (hidden) to keep that
+// source's entry points to itself.
+#ifndef PH_EXPORT
 #define PH_EXPORT extern "C" __attribute__((visibility("default")))
+#endif
 
 namespace ph {
 

@@ -93,7 +93,12 @@ void Engine::validate(const std::vector<StepEntry>& entries) const {
 //   tokens [T] | positions [columns, T] | row_seg [T] | seg_start [S + 1] | ctx_len [S] | slot [S] | want [>= 1]
 //   | per group block_table [S, width] | per group slot_mapping [T] | decode_rows [>= 1] | what the parts added
 void Engine::layout(const std::vector<StepEntry>& entries, int table_width, bool all_rows_wanted, Layout& lay) {
-    CacheManager& cache = *cache_;
+    lay_out_step(*cache_, model_->spec().position_columns, entries, table_width, all_rows_wanted,
+                 [&](StepPlan& plan) { model_->prepare_step(plan); }, lay);
+}
+
+void lay_out_step(CacheManager& cache, int cols, const std::vector<StepEntry>& entries, int table_width, bool all_rows_wanted,
+                  const std::function<void(StepPlan&)>& prepare, StepLayout& lay) {
     size_t reserved = 0;
     try {
         for (; reserved < entries.size(); reserved++) cache.reserve(entries[reserved].request, entries[reserved].n_tokens);
@@ -102,7 +107,7 @@ void Engine::layout(const std::vector<StepEntry>& entries, int table_width, bool
         for (size_t i = 0; i < reserved; i++) cache.unreserve(entries[i].request);
         throw;
     }
-    const int S = (int)entries.size(), G = (int)cache.groups().size(), cols = model_->spec().position_columns;
+    const int S = (int)entries.size(), G = (int)cache.groups().size();
     int T = 0;
     for (const StepEntry& e : entries) T += e.n_tokens;
     lay.T = T; lay.S = S;
@@ -135,8 +140,8 @@ void Engine::layout(const std::vector<StepEntry>& entries, int table_width, bool
     }
     // what the parts want to add
     StepPlan plan;
-    plan.T = T; plan.S = S; plan.q_lens = lay.q_lens; plan.ctx_lens = lay.ctx_lens; plan.starts = starts;
-    model_->prepare_step(plan);
+    plan.T = T; plan.S = S; plan.q_lens = lay.q_lens; plan.ctx_lens = lay.ctx_lens; plan.starts = starts; plan.slots = lay.slots;
+    if (prepare) prepare(plan);
 
     std::vector<int32_t>& f = lay.flat;
     f.clear();
@@ -193,12 +198,23 @@ void Engine::upload(const Layout& lay, void* device) {
 }
 
 void Engine::context(const Layout& lay, const int32_t* dev, Workspace& ws, StepContext& ctx, const int32_t** want_rows) {
-    const int G = (int)cache_->groups().size();
+    context_from_layout(lay, *cache_, model_->spec().position_columns, dev, ctx, want_rows);
+    ctx.workspace = &ws;
+    ctx.compute_dtype = model_->compute_dtype();
+    ctx.stream = stream_;
+    ctx.gemm_error = static_cast<int*>(error_words_.data());
+    ctx.attention_error = static_cast<int*>(error_words_.data()) + 1;
+    ctx.options = &options_.step_options;
+}
+
+void context_from_layout(const StepLayout& lay, const CacheManager& cache, int position_columns, const int32_t* dev, StepContext& ctx,
+                         const int32_t** want_rows) {
+    const int G = (int)cache.groups().size();
     auto at = [&](int i) { return dev + lay.offset[i]; };
     ctx.T = lay.T; ctx.S = lay.S;
     ctx.token_ids = at(0);
     ctx.positions = at(1);
-    ctx.position_columns = model_->spec().position_columns;
+    ctx.position_columns = position_columns;
     ctx.row_seg = at(2);
     ctx.seg_start = at(3);
     ctx.seg_ctx_len = at(4);
@@ -211,22 +227,16 @@ void Engine::context(const Layout& lay, const int32_t* dev, Workspace& ws, StepC
         gs.block_table = at(7 + g);
         gs.table_width = lay.widths[g];
         gs.slot_mapping = at(7 + G + g);
-        gs.page_size = cache_->page_size();
+        gs.page_size = cache.page_size();
         ctx.groups.push_back(gs);
     }
-    ctx.workspace = &ws;
-    ctx.compute_dtype = model_->compute_dtype();
-    ctx.stream = stream_;
     ctx.decode_only = lay.n_portions == 0;
     ctx.decode_rows = ctx.decode_only ? nullptr : at(7 + 2 * G);
     ctx.n_decode_rows = lay.n_decode;
     ctx.decode_max_ctx = bucket(lay.decode_max_ctx);
     ctx.prefill_max_ctx = bucket(lay.prefill_max_ctx);
-    ctx.gemm_error = static_cast<int*>(error_words_.data());
-    ctx.attention_error = static_cast<int*>(error_words_.data()) + 1;
     ctx.arrays.clear();
     for (const auto& a : lay.extra) ctx.arrays[a.first] = StepArray{dev + a.second.first, a.second.second};
-    ctx.options = &options_.step_options;
 }
 
 Tensor Engine::forward(StepContext& ctx, const int32_t* want_rows, int n_want) {

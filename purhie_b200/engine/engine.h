@@ -65,6 +65,27 @@ struct PendingTokens {
     cudaEvent_t event = nullptr;
 };
 
+// A step as the host lays it out: one int32 buffer
+//   tokens [T] | positions [columns, T] | row_seg [T] | seg_start [S + 1] | ctx_len [S] | slot [S] | want [>= 1]
+//   | per group block_table [S, width] | per group slot_mapping [T] | decode_rows [>= 1] | what the parts added
+// and the host's own copies of what launch decisions need.
+struct StepLayout {
+    std::vector<int32_t> flat;
+    std::vector<size_t> offset;                      // of each fixed array in flat
+    std::vector<std::pair<std::string, std::pair<size_t, int>>> extra;    // part arrays: name -> (offset, count)
+    int T = 0, S = 0, n_want = 0, n_decode = 0, n_portions = 0, decode_max_ctx = 0, prefill_max_ctx = 0;
+    std::vector<int> widths, q_lens, ctx_lens, slots;
+};
+// Reserve pages for the batch (all or nothing: OutOfPages leaves the cache as it was), let `prepare` add the parts'
+// own arrays, and lay everything out.  all_rows_wanted: the wanted rows are every entry's first row (a batch of
+// single tokens whose graph computes all logits).
+QE_API void lay_out_step(CacheManager& cache, int position_columns, const std::vector<StepEntry>& entries, int table_width,
+                         bool all_rows_wanted, const std::function<void(StepPlan&)>& prepare, StepLayout& lay);
+// The step context over a layout that lies at `dev` on the device (workspace, stream, dtype and error words are the
+// caller's to fill in).
+QE_API void context_from_layout(const StepLayout& lay, const CacheManager& cache, int position_columns, const int32_t* dev,
+                                StepContext& ctx, const int32_t** want_rows);
+
 class QE_API Engine {
 public:
     Engine(std::shared_ptr<DecoderModel> model, const EngineOptions& options);
@@ -124,13 +145,7 @@ public:
     EngineOptions& options() { return options_; }
 
 private:
-    struct Layout {
-        std::vector<int32_t> flat;
-        std::vector<size_t> offset;                      // of each fixed array in flat
-        std::vector<std::pair<std::string, std::pair<size_t, int>>> extra;    // part arrays: name -> (offset, count)
-        int T = 0, S = 0, n_want = 0, n_decode = 0, n_portions = 0, decode_max_ctx = 0, prefill_max_ctx = 0;
-        std::vector<int> widths, q_lens, ctx_lens, slots;
-    };
+    using Layout = StepLayout;
     struct Graph {
         Workspace workspace;
         DeviceBuffer meta;

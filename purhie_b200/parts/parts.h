@@ -195,6 +195,7 @@ struct StepContext {
 struct StepPlan {
     int T = 0, S = 0;
     std::vector<int> q_lens, ctx_lens, starts;      // per segment: new tokens, tokens afterwards, first new position
+    std::vector<int> slots;                         // per segment: the state slot of its request
     std::vector<std::pair<std::string, std::vector<int32_t>>> arrays;
     bool has(const std::string& name) const { for (const auto& a : arrays) if (a.first == name) return true; return false; }
     void add(const std::string& name, std::vector<int32_t> values) { arrays.emplace_back(name, std::move(values)); }

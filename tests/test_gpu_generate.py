@@ -307,8 +307,8 @@ def test_qwen_demo_command_line(models, tmp_path):
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
     rows = [l for l in r.stdout.splitlines() if l.startswith("Request ")]
-    assert [int(x) for x in rows[0].split(":")[1].split()] == exp
-    assert [int(x) for x in rows[1].split(":")[1].split()] == plain_greedy(pc, pw, other, 5)
+    assert [int(x) for x in rows[0].split("):")[1].split()] == exp
+    assert [int(x) for x in rows[1].split("):")[1].split()] == plain_greedy(pc, pw, other, 5)
     assert "Timing: 2 requests, 65 prompt tokens and 10 generated tokens" in r.stdout
     # random weights from a configuration file: the tokens of the folder written with the same seed
     cfg_path = tmp_path / "config.json"

@@ -3,8 +3,9 @@ memory (a server whose memory is all handed out, a host that links the C symbols
 latency path that cannot afford cudaMalloc's synchronisation).  It keeps its scratch in a fixed array inside the
 library, so this test calls it the way such a caller would: through the exported C symbol with raw pointers,
 twice in a row on one stream (the second call finds the first call's leftovers in the array), and compares
-each result with the ordinary entry point, which gets scratch from the test.  It also checks that a request
-larger than the array is refused by name instead of overrunning it.
+each result with the ordinary entry point, which gets scratch from the test, and with attention computed densely
+in float64.  It also checks that a request larger than the array is refused by name instead of overrunning it,
+and that a call that needs no scratch (keys in one piece) is not refused whatever its size.
 
 The file sorts last on purpose: a run that stops at the first failure has then run every other test.
 """
@@ -74,6 +75,10 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         diff = (got.float() - ref.float()).abs().max().item()
         assert diff <= 1e-2 * ref.float().abs().max().item(), diff       # the tolerance of the attention kernel tests
         assert torch.equal(got, ref)                                      # and in fact the same kernels: the same bits
+        # the math itself, against attention computed densely in float64
+        from test_gpu_kernels import dense_attention
+        dense = dense_attention(case, c["HQ"], c["HKV"], c["D"], c["window"], scale)
+        assert (got.double().cpu() - dense).abs().max().item() <= 1e-2 * dense.abs().max().item()
 
 
 def test_static_scratch_entry_point_refuses_more_than_its_array_holds():
@@ -87,3 +92,21 @@ def test_static_scratch_entry_point_refuses_more_than_its_array_holds():
     msg = err().decode()
     assert "16777216" in msg and "scratch" in msg
     torch.cuda.synchronize()
+
+
+def test_static_scratch_entry_point_takes_any_size_when_the_keys_are_in_one_piece():
+    """With one split the kernel writes its result directly and uses no scratch: 3,000 rows x 8 heads would need 12 MiB
+    at four splits and is far beyond the array at 32, but at one split nothing is needed and nothing is refused."""
+    from test_gpu_kernels import dense_attention
+    fn, err = _entry()
+    HQ, HKV, D, ps = 8, 2, 128, 16
+    case = _case([(70 + (i % 50), 1) for i in range(3000)], HQ, HKV, D, ps, 24)
+    scale = 1.0 / math.sqrt(D)
+    rc, got = _call_static(fn, case, HQ, HKV, D, ps, 1, None, scale)
+    assert rc == 0, err().decode()
+    ref = _call_ordinary(case, HQ, HKV, D, ps, 1, None, scale)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ref)
+    few = dict(case, T=16, segs=case["segs"][:16], dense=case["dense"][:16])
+    dense = dense_attention(few, HQ, HKV, D, None, scale)
+    assert (got[:16].double().cpu() - dense).abs().max().item() <= 1e-2 * dense.abs().max().item()
