@@ -387,6 +387,14 @@ API int qe_time_step(inference_model_t* m, const engine_step_batch* batch, doubl
     });
 }
 
+// Time per kernel class (see LaunchProfile in host/device.h): on with PURHIE_PROFILE=1 in the environment or with
+// qe_profile_enable(1).  The report is {"launcher": {"calls", "ms", "bytes", "flops"}} since the last reset.
+API void qe_profile_enable(int on) { LaunchProfile::get().set_enabled(on != 0); }
+API int qe_profile_enabled(void) { return LaunchProfile::get().on() ? 1 : 0; }
+API const char* qe_profile_report(int reset) {
+    return guarded_text([&] { return LaunchProfile::get().report_json(reset != 0); });
+}
+
 API long long qe_launches(void) { return g_launches; }
 API void qe_set_library_dir(const char* dir) { set_library_dir(dir ? dir : ""); }
 

@@ -15,6 +15,8 @@ prompt they all run at once through the request queue (``--max-batch-tokens``: t
 ``--block-size`` is the number of tokens per cache page.  Generation stops at an end-of-generation token of the
 model's configuration unless ``--ignore-eos``.  The options of the reference that belong to parts that are not built
 (``--lm-head-q8``, ``--draft``, ``--drafts``, ``--kv-q8``, ``--kv-q4``, ``--stage``) are refused by name.
+With ``PURHIE_PROFILE=1`` in the environment the device time per kernel class is printed at the end (the reference
+prints its breakdown under ``QWEN_PROFILE=1``).
 """
 from __future__ import annotations
 
@@ -163,6 +165,9 @@ def main(argv=None) -> int:
     except (InferenceError, OSError, ValueError) as e:
         sys.stderr.write(f"qwen_demo: {e}\n")
         return 1
+    from . import native
+    if native.profile_enabled():             # PURHIE_PROFILE=1: where the device time went, per kernel class
+        sys.stderr.write(native.format_profile(native.profile_report(), "prefill and generation") + "\n")
     pre_ms, gen_ms = (t1 - t0) * 1e3, (t2 - t1) * 1e3
     print(f"Timing: prefill {n_prompt} tokens {pre_ms:.1f} ms ({n_prompt / max(pre_ms, 1e-9) * 1e3:.1f} tok/s), "
           f"generation {n_out} tokens {gen_ms:.1f} ms ({n_out / max(gen_ms, 1e-9) * 1e3:.1f} tok/s), stop: {reason}")

@@ -240,6 +240,7 @@ void context_from_layout(const StepLayout& lay, const CacheManager& cache, int p
 }
 
 Tensor Engine::forward(StepContext& ctx, const int32_t* want_rows, int n_want) {
+    if (LaunchProfile::get().on()) LaunchProfile::get().set_stream(stream_);
     if (!layer_dump_) return model_->forward(ctx, views_, want_rows, n_want);
     auto dump = [&](int entry, ResidualStream& stream, StepContext& c) {
         const int T = c.T, E = (int)stream.x.shape[1];
@@ -266,7 +267,7 @@ Tensor Engine::forward(StepContext& ctx, const int32_t* want_rows, int n_want) {
 }
 
 bool Engine::decodes_as_graph(const std::vector<StepEntry>& entries) const {
-    if (!options_.cuda_graphs || layer_dump_ || (int)entries.size() > options_.max_graph_batch) return false;
+    if (!options_.cuda_graphs || layer_dump_ || LaunchProfile::get().on() || (int)entries.size() > options_.max_graph_batch) return false;
     for (const StepEntry& e : entries) if (e.n_tokens != 1) return false;
     return true;
 }

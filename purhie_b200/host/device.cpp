@@ -195,6 +195,68 @@ void require_library(const std::string& name) {
     }
 }
 
+// ---- time per kernel class ----------------------------------------------------------------------------------------
+LaunchProfile::LaunchProfile() {
+    const char* e = getenv("PURHIE_PROFILE");
+    enabled_ = e && *e && *e != '0';
+}
+LaunchProfile& LaunchProfile::get() {
+    static LaunchProfile p;
+    return p;
+}
+void LaunchProfile::begin(const char* call_text) {
+    // "k.add_rmsnorm(stream.x, ...)" -> "add_rmsnorm"
+    std::string name(call_text);
+    size_t paren = name.find('(');
+    if (paren != std::string::npos) name.resize(paren);
+    size_t dot = name.rfind('.');
+    if (dot != std::string::npos) name = name.substr(dot + 1);
+    Record r;
+    r.name = name;
+    r.bytes = pending_bytes_; r.flops = pending_flops_;
+    pending_bytes_ = pending_flops_ = 0;
+    if (spare_.empty()) {
+        cudaEventCreate(&r.start);
+        cudaEventCreate(&r.stop);
+    } else {
+        r.start = spare_.back().first; r.stop = spare_.back().second;
+        spare_.pop_back();
+    }
+    cudaEventRecord(r.start, stream_);
+    records_.push_back(r);
+    if (records_.size() > 65536) fold();
+}
+void LaunchProfile::end() {
+    if (!records_.empty()) cudaEventRecord(records_.back().stop, stream_);
+}
+void LaunchProfile::fold() {
+    cudaStreamSynchronize(stream_);
+    for (Record& r : records_) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess) {
+            Sum& s = sums_[r.name];
+            s.calls++; s.ms += ms; s.bytes += r.bytes; s.flops += r.flops;
+        }
+        spare_.emplace_back(r.start, r.stop);
+    }
+    records_.clear();
+}
+std::string LaunchProfile::report_json(bool reset) {
+    fold();
+    std::string out = "{";
+    bool first = true;
+    for (const auto& kv : sums_) {
+        char buf[256];
+        snprintf(buf, sizeof buf, "%s\"%s\": {\"calls\": %lld, \"ms\": %.6f, \"bytes\": %.0f, \"flops\": %.0f}", first ? "" : ", ",
+                 kv.first.c_str(), kv.second.calls, kv.second.ms, kv.second.bytes, kv.second.flops);
+        out += buf;
+        first = false;
+    }
+    out += "}";
+    if (reset) sums_.clear();
+    return out;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

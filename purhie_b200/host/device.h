@@ -135,10 +135,46 @@ QE_API const GemmKernels& gemm_kernels();
 QE_API void require_library(const std::string& name);      // "core", "flash", "gemm100": open it now
 QE_API extern long long g_launches;                          // launcher calls so far (for the bench's count)
 
+// Time per kernel class, for finding out where a step's time goes (the reference prints such a breakdown under
+// QWEN_PROFILE=1: src/qwen_model.cpp:393-423, 2795-2818).  Off unless PURHIE_PROFILE=1 is in the environment (or
+// set_enabled): then every launcher call is bracketed by CUDA events on the engine's stream, batches of single
+// tokens are launched kernel by kernel instead of replayed as graphs, and report() gives, per launcher name, the
+// calls, the device milliseconds and, where the caller noted them, the bytes and flops of its launches.  The
+// events serialise nothing, but a profiled step is a little slower than an unprofiled one.
+class QE_API LaunchProfile {
+public:
+    static LaunchProfile& get();
+    bool on() const { return enabled_; }
+    void set_enabled(bool on) { enabled_ = on; }
+    void set_stream(cudaStream_t s) { stream_ = s; }
+    void note_cost(double bytes, double flops) { pending_bytes_ = bytes; pending_flops_ = flops; }   // of the next launch
+    void begin(const char* call_text);
+    void end();
+    // {"name": {"calls", "ms", "bytes", "flops"}} over everything since the last reset; waits for the stream.
+    std::string report_json(bool reset);
+private:
+    LaunchProfile();
+    struct Record { std::string name; cudaEvent_t start, stop; double bytes, flops; };
+    bool enabled_ = false;
+    cudaStream_t stream_ = nullptr;
+    double pending_bytes_ = 0, pending_flops_ = 0;
+    std::vector<Record> records_;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> spare_;
+    struct Sum { long long calls = 0; double ms = 0, bytes = 0, flops = 0; };
+    std::map<std::string, Sum> sums_;
+    void fold();
+};
+struct LaunchScope {
+    bool on;
+    explicit LaunchScope(const char* call_text) : on(LaunchProfile::get().on()) { if (on) LaunchProfile::get().begin(call_text); }
+    ~LaunchScope() { if (on) LaunchProfile::get().end(); }
+};
+
 // Run a launcher; a non-zero status becomes a KernelError with the library's text.
 #define QE_LAUNCH(lib, call)                                                                     \
     do {                                                                                         \
         ::qe::g_launches++;                                                                      \
+        ::qe::LaunchScope qe_scope_(#call);                                                      \
         if ((call) != 0) throw ::qe::KernelError((lib).last_error());                           \
     } while (0)
 

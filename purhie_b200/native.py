@@ -205,6 +205,9 @@ _SIGNATURES = {
     "qe_time_step": (c_int, [_P, POINTER(StepBatchC), POINTER(c_double)]),
     "qe_time_decode_steps": (c_int, [_P, POINTER(c_longlong), c_int, POINTER(c_int32), c_int, c_int, c_int, POINTER(c_double),
                                      POINTER(c_longlong)]),
+    "qe_profile_enable": (None, [c_int]),
+    "qe_profile_enabled": (c_int, []),
+    "qe_profile_report": (c_char_p, [c_int]),
     "qe_launches": (c_longlong, []),
     "qe_set_library_dir": (None, [c_char_p]),
 }
@@ -275,6 +278,29 @@ def ensure_libraries_for(model_handle) -> None:
     """Compile the kernel libraries the loaded model launches from (they are opened by the host library itself)."""
     for name in answer(lib().qe_model_required_libraries(model_handle)):
         build_library(name)
+
+
+def profile_enabled() -> bool:
+    return bool(lib().qe_profile_enabled())
+
+
+def profile_report(reset: bool = True) -> dict:
+    """Time per kernel class since the last reset: {launcher: {"calls", "ms", "bytes", "flops"}} (empty unless
+    PURHIE_PROFILE=1 is in the environment or ``lib().qe_profile_enable(1)`` was called)."""
+    return answer(lib().qe_profile_report(int(reset)))
+
+
+def format_profile(report: dict, title: str = "forward") -> str:
+    """The report as lines: per launcher its calls, milliseconds, share of the total, and GB/s and TFLOP/s where the
+    launches' bytes and flops are known."""
+    total = sum(v["ms"] for v in report.values()) or 1e-12
+    lines = [f"[profile] {title}: {sum(v['calls'] for v in report.values())} launches, {total:.3f} ms on the device"]
+    for name, v in sorted(report.items(), key=lambda kv: -kv[1]["ms"]):
+        line = f"[profile]   {name:<24} {v['calls']:>7} calls {v['ms']:>10.3f} ms {100 * v['ms'] / total:>5.1f}%"
+        if v["bytes"] > 0 and v["ms"] > 0:
+            line += f"  {v['bytes'] / v['ms'] / 1e6:>8.1f} GB/s  {v['flops'] / v['ms'] / 1e9:>8.1f} TFLOP/s"
+        lines.append(line)
+    return "\n".join(lines)
 
 
 def int32_array(values):

@@ -95,6 +95,8 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
     }
     if (!(fast_ && x.dtype == DType::BF16)) {
         Tensor out = ws.get(out_name, {M, N}, out_dtype);
+        if (LaunchProfile::get().on())
+            LaunchProfile::get().note_cost((double)weight_.bytes() + (double)x.bytes() + (double)out.bytes(), 2.0 * M * N * K);
         QE_LAUNCH(core, core.gemm_simple(x.data, x.code(), weight_.data, weight_.code(), out.data, out.code(), M, N, K, ctx.stream));
         return Addend(out, 1);
     }
@@ -102,6 +104,8 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
     const bool fused = fuse_swiglu && N % 2 == 0;
     GemmPlan p = plan_gemm(M, N, K, sm_count(), allow_split, fused);
     auto run = [&](Tensor& out, int splits, bool swiglu, bool accumulate) {
+        if (LaunchProfile::get().on())      // what the product has to move and to compute: the weight once, x, and its result
+            LaunchProfile::get().note_cost(2.0 * N * K + 2.0 * M * K + (double)out.bytes(), 2.0 * M * N * K);
         if (p.pair)
             QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, splits, 0, swiglu, accumulate,
                                      ctx.gemm_error, ctx.stream));

@@ -299,6 +299,16 @@ def test_qwen_demo_command_line(models, tmp_path):
         assert lines[-1].startswith("Timing: prefill 20 tokens")
     r = subprocess.run(demo + [folder, "1,2", "--kv-q8"], capture_output=True, text=True)
     assert r.returncode == 1 and "--kv-q8" in r.stderr
+    # with PURHIE_PROFILE=1 the same tokens, and the device time per kernel class at the end
+    r = subprocess.run(demo + [folder, ",".join(map(str, prompt)), "5", "--dtype", "float32", "--ctx", "128"], capture_output=True,
+                       text=True, timeout=300, env=dict(os.environ, PURHIE_PROFILE="1"))
+    assert r.returncode == 0, r.stderr
+    assert [int(x) for x in r.stdout.strip().splitlines()[2:7]] == exp
+    prof = [l for l in r.stderr.splitlines() if l.startswith("[profile]")]
+    names = {l.split()[1] for l in prof[1:]}
+    assert {"gemm_simple", "add_rmsnorm", "qk_norm_rope_kv_write", "attention_generic", "embed_gather", "argmax"} <= names
+    gemm = next(l for l in prof if " gemm_simple " in l)
+    assert "GB/s" in gemm and "TFLOP/s" in gemm               # the products note their bytes and flops
     # several prompts, one a line, through the request queue with a small budget and a small page
     other = random_tokens(45, cfg.vocab_size, 34)
     (tmp_path / "many.txt").write_text(" ".join(map(str, prompt)) + "\n" + ",".join(map(str, other)) + "\n")

@@ -145,3 +145,51 @@ def test_float32_at_the_8b_layer_shape_agrees_with_the_plain_implementation(tmp_
                 assert np.array_equal(got.numpy(), whole), f"{name}: float32 is not bit-equal across the cuts"
             else:
                 assert not same_top1_or_near_tie(got, ref, tol), f"{dtype}/{name}: argmax differs away from a tie"
+
+
+def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
+    """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
+    8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
+    from purhie_b200.engine import Engine, StepEntry
+    reqs = [ids(30 + (i * 211) % 1471 + 6, 300 + i) for i in range(64)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(SHAPES["8b"], 7, dtype=dtype, page_size=16, max_tokens=65 * 1536, max_requests=64)
+        for i, r in enumerate(reqs):
+            eng.add_request(i)
+            eng.step([StepEntry(i, r[:-6], [])])
+        rows = [eng.step([StepEntry(i, [r[len(r) - 6 + k]], [0]) for i, r in enumerate(reqs)]) for k in range(6)]
+        assert eng.info()["graph_replays"] >= 4
+        got[dtype] = np.stack(rows)
+        eng.close()
+    err = rel(got["bfloat16"], got["float32"])
+    assert err < 3e-2 and not np.isnan(got["bfloat16"]).any()
+    per_request = [rel(got["bfloat16"][:, i], got["float32"][:, i]) for i in range(64)]
+    assert max(per_request) < 6e-2, (int(np.argmax(per_request)), max(per_request))
+
+
+def test_twenty_thousand_tokens_through_one_layer():
+    """One 8B-class layer over 20,000 tokens: whole, in portions of 4,096, decoding after it and a late short portion.
+    float32 gives the same bits however it is cut; bfloat16 stays within a percent of it."""
+    from purhie_b200.engine import Engine, StepEntry
+    shape = dict(SHAPES["8b"], num_hidden_layers=1, max_position_embeddings=32768, vocab_size=8000)
+    toks = ids(20040, 17, vocab=8000)
+    N = 20000
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(shape, 9, dtype=dtype, page_size=16, max_tokens=3 * 20480, max_requests=3)
+        eng.add_request("whole"); eng.add_request("cut")
+        res = {"whole": eng.step([StepEntry("whole", toks[:N], [N - 1])])}
+        for s in range(0, N, 4096):
+            part = toks[s:min(s + 4096, N)]
+            lg = eng.step([StepEntry("cut", part, [len(part) - 1] if s + 4096 >= N else [])])
+        res["cut"] = lg
+        res["decode"] = np.concatenate([eng.step([StepEntry("cut", toks[N + k:N + k + 1], [0])]) for k in range(8)])
+        res["late"] = eng.step([StepEntry("whole", toks[N:N + 40], [7, 39])])
+        got[dtype] = res
+        eng.close()
+    f32, b16 = got["float32"], got["bfloat16"]
+    assert np.array_equal(f32["whole"], f32["cut"])
+    assert np.array_equal(f32["late"][0], f32["decode"][7])                 # position 20,007 either way
+    for name in ("whole", "cut", "decode", "late"):
+        assert rel(b16[name], f32[name]) < 1e-2, name
