@@ -391,6 +391,9 @@ API int qe_time_step(inference_model_t* m, const engine_step_batch* batch, doubl
 // qe_profile_enable(1).  The report is {"launcher": {"calls", "ms", "bytes", "flops"}} since the last reset.
 API void qe_profile_enable(int on) { LaunchProfile::get().set_enabled(on != 0); }
 API int qe_profile_enabled(void) { return LaunchProfile::get().on() ? 1 : 0; }
+// Timing by omission: the launchers named (comma separated; "" for none) are skipped from now on.  For finding what
+// a kernel class costs inside a graph; the results of a step are meaningless while anything is left out.
+API void qe_profile_leave_out(const char* names) { LaunchProfile::get().leave_out(names); }
 API const char* qe_profile_report(int reset) {
     return guarded_text([&] { return LaunchProfile::get().report_json(reset != 0); });
 }

@@ -379,23 +379,44 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
 template <int D>
 __global__ void attention_combine_bulk_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int32_t* __restrict__ row_list, __nv_bfloat16* __restrict__ out, int HQ, int splits) {
+    // One block per (row, head), a thread per element of the head.  Lane s of every warp fetches the maximum and sum
+    // of split s, so that the weights of 32 splits cost one round trip, and the partial outputs are fetched eight
+    // splits at a time; the sums run over the splits in ascending order whatever the block's shape.
     pdl_launch_dependents();
     pdl_wait();
-    const int i = blockIdx.x, h = blockIdx.y;
+    const int i = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31;
     const int t = row_list ? row_list[i] : i;
     const size_t slot0 = ((size_t)i * HQ + h) * splits;
     float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(slot0 + s) * 2]);
-    const float use = mm == -INFINITY ? 0.0f : mm;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f, ll = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float c = exp2f(part_ml[(slot0 + s) * 2] - use);
-            acc += c * part_o[(slot0 + s) * D + d];
-            ll += c * part_ml[(slot0 + s) * 2 + 1];
-        }
-        out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        float m = s0 + lane < splits ? part_ml[(slot0 + s0 + lane) * 2] : -INFINITY;
+#pragma unroll
+        for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        mm = fmaxf(mm, m);
     }
+    const float use = mm == -INFINITY ? 0.0f : mm;
+    const int d = threadIdx.x;                              // blockDim.x == min(D, 128); D <= 128 here
+    float acc = 0.0f, ll = 0.0f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        const int n = min(32, splits - s0);
+        float c = 0.0f, cl = 0.0f;
+        if (lane < n) {
+            c = exp2f(part_ml[(slot0 + s0 + lane) * 2] - use);
+            cl = c * part_ml[(slot0 + s0 + lane) * 2 + 1];
+        }
+        const float* po = part_o + (slot0 + s0) * D + d;
+        for (int j = 0; j < n; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = j + u < n ? po[(size_t)(j + u) * D] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                acc += __shfl_sync(0xffffffffu, c, (j + u) & 31) * v[u];      // lanes >= n hold zero
+                ll += __shfl_sync(0xffffffffu, cl, (j + u) & 31);
+            }
+        }
+    }
+    out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
 }
 
 int sm_count() {

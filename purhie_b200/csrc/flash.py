@@ -156,8 +156,8 @@ def bulk_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: 
     """Splits for the persistent kernel: two CTAs per SM take items in turn, so the time is (items per CTA, rounded
     up) x (blocks of 64 keys per item + what an item costs beside its blocks), plus the merge kernel when the keys
     are split; pick the split count that minimises it.  A split item costs about a block and a half more (its
-    partial result goes to memory), a whole one next to nothing: measured at 16 to 128 rows of 1,024 to 4,096
-    keys, where the count this picks was the fastest or within 3 % of it."""
+    partial result goes to memory), a whole one next to nothing, and the merge grows with the number of parts it
+    reads: measured at 1 to 128 rows of 1,024 to 8,192 keys."""
     span = min(max_ctx, window) if window else max_ctx
     blocks = max(1, -(-span // BLOCK_KEYS))
     pairs = max(1, n_rows * num_kv_heads)
@@ -166,7 +166,7 @@ def bulk_splits(n_rows: int, num_kv_heads: int, max_ctx: int, sms: int, window: 
         per = -(-blocks // s)
         if s > 1 and -(-blocks // per) != s:
             continue
-        cost = -(-(pairs * s) // (2 * sms)) * (per + (1.5 if s > 1 else 0.25)) + (2.0 if s > 1 else 0.0)
+        cost = -(-(pairs * s) // (2 * sms)) * (per + (1.5 if s > 1 else 0.25)) + (2.0 + 0.15 * s if s > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

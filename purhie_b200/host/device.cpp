@@ -204,15 +204,35 @@ LaunchProfile& LaunchProfile::get() {
     static LaunchProfile p;
     return p;
 }
-void LaunchProfile::begin(const char* call_text) {
+std::string LaunchProfile::launcher_name(const char* call_text) {
     // "k.add_rmsnorm(stream.x, ...)" -> "add_rmsnorm"
     std::string name(call_text);
     size_t paren = name.find('(');
     if (paren != std::string::npos) name.resize(paren);
     size_t dot = name.rfind('.');
     if (dot != std::string::npos) name = name.substr(dot + 1);
+    return name;
+}
+void LaunchProfile::leave_out(const char* names) {
+    left_out_.clear();
+    std::string all(names ? names : "");
+    size_t at = 0;
+    while (at <= all.size()) {
+        size_t comma = all.find(',', at);
+        if (comma == std::string::npos) comma = all.size();
+        if (comma > at) left_out_.push_back(all.substr(at, comma - at));
+        at = comma + 1;
+    }
+}
+bool LaunchProfile::is_left_out(const char* call_text) const {
+    const std::string name = launcher_name(call_text);
+    for (const std::string& n : left_out_)
+        if (n == name) return true;
+    return false;
+}
+void LaunchProfile::begin(const char* call_text) {
     Record r;
-    r.name = name;
+    r.name = launcher_name(call_text);
     r.bytes = pending_bytes_; r.flops = pending_flops_;
     pending_bytes_ = pending_flops_ = 0;
     if (spare_.empty()) {

@@ -152,7 +152,14 @@ public:
     void end();
     // {"name": {"calls", "ms", "bytes", "flops"}} over everything since the last reset; waits for the stream.
     std::string report_json(bool reset);
+    // Timing by omission: launchers named here (comma separated, "" for none) are not run from now on, so that a
+    // graph captured afterwards shows what the rest costs without them.  The step's results are then meaningless.
+    void leave_out(const char* names);
+    bool leaves_out(const char* call_text) const { return !left_out_.empty() && is_left_out(call_text); }
 private:
+    bool is_left_out(const char* call_text) const;
+    std::vector<std::string> left_out_;
+    static std::string launcher_name(const char* call_text);
     LaunchProfile();
     struct Record { std::string name; cudaEvent_t start, stop; double bytes, flops; };
     bool enabled_ = false;
@@ -175,6 +182,7 @@ struct LaunchScope {
     do {                                                                                         \
         ::qe::g_launches++;                                                                      \
         ::qe::LaunchScope qe_scope_(#call);                                                      \
+        if (::qe::LaunchProfile::get().leaves_out(#call)) break;                                 \
         if ((call) != 0) throw ::qe::KernelError((lib).last_error());                           \
     } while (0)
 

@@ -207,6 +207,7 @@ _SIGNATURES = {
                                      POINTER(c_longlong)]),
     "qe_profile_enable": (None, [c_int]),
     "qe_profile_enabled": (c_int, []),
+    "qe_profile_leave_out": (None, [c_char_p]),
     "qe_profile_report": (c_char_p, [c_int]),
     "qe_launches": (c_longlong, []),
     "qe_set_library_dir": (None, [c_char_p]),

@@ -50,7 +50,8 @@ int decode_splits(int n_rows, int kv_heads, int max_ctx, int sms, int window) {
 // Splits for the persistent kernel: two CTAs per SM take items in turn, so the time is (items per CTA, rounded
 // up) x (blocks of 64 keys per item + what an item costs beside its blocks), plus the merge kernel when the keys
 // are split.  A split item costs about a block and a half more (its partial result goes to memory), a whole one
-// next to nothing: measured at 16 to 128 rows of 1,024 to 4,096 keys.
+// next to nothing, and the merge grows with the number of parts it reads: measured at 1 to 128 rows of 1,024 to
+// 8,192 keys.
 int bulk_splits(int n_rows, int kv_heads, int max_ctx, int sms, int window) {
     const int span = window ? std::min(max_ctx, window) : max_ctx;
     const int blocks = std::max(1, ceil_div(span, kBlockKeys)), pairs = std::max(1, n_rows * kv_heads);
@@ -59,7 +60,7 @@ int bulk_splits(int n_rows, int kv_heads, int max_ctx, int sms, int window) {
     for (int s = 1; s <= std::min(blocks, kMaxSplits); s++) {
         const int per = ceil_div(blocks, s);
         if (s > 1 && ceil_div(blocks, per) != s) continue;
-        const double cost = (double)ceil_div((long long)pairs * s, 2 * sms) * (per + (s > 1 ? 1.5 : 0.25)) + (s > 1 ? 2.0 : 0.0);
+        const double cost = (double)ceil_div((long long)pairs * s, 2 * sms) * (per + (s > 1 ? 1.5 : 0.25)) + (s > 1 ? 2.0 + 0.15 * s : 0.0);
         if (best_cost < 0 || cost < best_cost - 1e-9) { best = s; best_cost = cost; }
     }
     return best;
