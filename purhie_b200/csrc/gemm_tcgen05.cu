@@ -171,7 +171,8 @@ template <int BN> struct TileConfig {
     static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : 2 * BN;          // a power of two: BN is one
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int STAGING_BYTES = 4 * 32 * 32 * 2;                   // per epilogue warp: 32 tokens x 32 features, bfloat16
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */ + STAGING_BYTES;
 };
 
 // One chunk of CH accumulator columns of row a, starting at column b0 + c of the tile, to its place in out.
@@ -288,6 +289,46 @@ __device__ __forceinline__ void store_chunk_swapped_swiglu(const GemmParams& p, 
     }
 }
 
+// Swapped orientation, bfloat16 output (plain or with the activation): the warp's 32 features x CH tokens go through
+// its own staging buffer in shared memory, [token][feature], and leave as 16-byte vectors along the features
+// instead of one 2-byte store per value.  With the activation, gate and up features are neighbouring lanes: the
+// even lane works out token j, the odd lane token j + 1 of every pair of tokens, after one exchange.
+// a_base: the warp's first output feature; every lane of the warp calls this.
+template <int CH>
+__device__ __forceinline__ void store_chunk_swapped_bf16(const GemmParams& p, const uint32_t* r, __nv_bfloat16* buf, int a_base,
+                                                         int lane, int b0, int c) {
+    const int W = p.swiglu ? 16 : 32;                 // output columns of this warp
+    if (p.swiglu) {
+        const int odd = lane & 1;
+#pragma unroll
+        for (int j = 0; j < CH; j += 2) {
+            const float m0 = __uint_as_float(r[j]), m1 = __uint_as_float(r[j + 1]);
+            const float got = __shfl_xor_sync(0xffffffffu, odd ? m0 : m1, 1);
+            const float gate = odd ? got : m0, up = odd ? m1 : got;
+            buf[(j + odd) * 16 + (lane >> 1)] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) buf[j * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+    __syncwarp();
+    const int vec_per_row = W / 8;
+    const int first = p.swiglu ? a_base / 2 : a_base, limit = p.swiglu ? p.rows_a / 2 : p.rows_a;
+    for (int idx = lane; idx < CH * vec_per_row; idx += 32) {
+        const int row = idx / vec_per_row, v = idx % vec_per_row;
+        const int token = b0 + c + row, col = first + v * 8;
+        if (token >= p.rows_b || col >= limit) continue;
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)token * p.ld + col;
+        const __nv_bfloat16* src = buf + row * W + v * 8;
+        if (col + 8 <= limit && ((uintptr_t)dst & 15) == 0) {
+            *(uint4*)dst = *(const uint4*)src;
+        } else {
+            for (int e = 0; e < 8 && col + e < limit; ++e) dst[e] = src[e];
+        }
+    }
+    __syncwarp();                                      // the buffer is written again for the next chunk
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, TileConfig<BN>::CTAS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -302,6 +343,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    __nv_bfloat16* staging = (__nv_bfloat16*)(smem + STAGES * Cfg::STAGE_BYTES + 256);    // [4 warps][32 x 32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -429,7 +471,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint32_t r[CH];
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
-                if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
+                if (p.swapped && p.out_bf16) store_chunk_swapped_bf16<CH>(p, r, staging + q * 32 * 32, a0 + q * 32, lane, b0, c);
+                else if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
                 else store_chunk<CH>(p, r, a, b0, c, split_off);
             }
             tc_fence_before();
@@ -710,7 +753,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     int grid = Cfg::CTAS_PER_SM * sm_count();
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
-    launch_overlapped(kernel, dim3(grid), dim3(NUM_THREADS), (size_t)Cfg::SMEM_BYTES, stream, ma, mb, p);
+    // the staging buffer of the bfloat16 epilogue lies last: launches that do not use it leave it out
+    const size_t bytes = (size_t)Cfg::SMEM_BYTES - (p.swapped && p.out_bf16 ? 0 : Cfg::STAGING_BYTES);
+    launch_overlapped(kernel, dim3(grid), dim3(NUM_THREADS), bytes, stream, ma, mb, p);
     return check_launch("gemm_tcgen05");
 }
 
