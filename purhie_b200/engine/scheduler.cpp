@@ -158,7 +158,6 @@ std::vector<Scheduler::Planned> Scheduler::plan(const std::set<GenRequest*>* onl
             budget -= n;
         }
         // 3. admissions, first come first served
-        bool retry = false;
         for (size_t w = 0; w < waiting_.size() && budget > 0 && (int)running_.size() < max_running_ && cache_.slots().num_free() > 0;) {
             GenRequest* r = waiting_[w];
             if (!takes_part(r)) {
@@ -193,9 +192,7 @@ std::vector<Scheduler::Planned> Scheduler::plan(const std::set<GenRequest*>* onl
             take(*r, n, free);
             plan.push_back({r, 0, n, n == known});
             budget -= n;
-            if (!only && false) retry = true;
         }
-        (void)retry;
         bool stuck = plan.empty() && !pool.empty();
         if (stuck) {
             // nobody can move: the pages are spread over half-done prompts; make room for the oldest
@@ -261,7 +258,6 @@ std::vector<StepEvent> Scheduler::step(const std::set<GenRequest*>* only) {
     std::vector<StepEntry> entries;
     std::vector<Sampler*> samplers;
     std::vector<GenRequest*> sampled;
-    static const int32_t kLast[1] = {0};
     std::vector<std::vector<int32_t>> want_store(planned.size());
     for (size_t i = 0; i < planned.size(); i++) {
         const Planned& p = planned[i];
@@ -278,7 +274,6 @@ std::vector<StepEvent> Scheduler::step(const std::set<GenRequest*>* only) {
         }
         entries.push_back(e);
     }
-    (void)kLast;
     std::vector<int> toks = runner_.run(entries, samplers);
     steps++;
     for (size_t i = 0; i < sampled.size(); i++) events.push_back(emit(sampled[i], toks[i]));

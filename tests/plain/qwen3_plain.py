@@ -126,9 +126,11 @@ def swiglu_mlp(x, w, prefix):
     return (g / (1.0 + torch.exp(-g)) * u) @ w[prefix + "mlp.down_proj.weight"].T
 
 
-def forward(cfg, w, tokens, return_hidden=False):
+def forward(cfg, w, tokens, return_hidden=False, layer_outputs=None):
     """Logits [T, V] (float64) for one whole sequence starting at position 0.  Layer order and residuals:
-    src/qwen_model.cpp:1196-1279; tied head when config says so: src/inference.cpp:1392-1396."""
+    src/qwen_model.cpp:1196-1279; tied head when config says so: src/inference.cpp:1392-1396.  A list given as
+    ``layer_outputs`` receives the residual stream after every layer (what the reference's per-layer callback sees,
+    src/qwen_model.cpp:1262-1275)."""
     eps = cfg.get("rms_norm_eps", 1e-6)
     positions = list(range(len(tokens)))
     x = embedding(w["model.embed_tokens.weight"], tokens)
@@ -137,6 +139,8 @@ def forward(cfg, w, tokens, return_hidden=False):
         p = f"model.layers.{l}."
         x = x + attention_block(rmsnorm(x, w[p + "input_layernorm.weight"], eps), w, p, cfg, positions, windows[l])
         x = x + swiglu_mlp(rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps), w, p)
+        if layer_outputs is not None:
+            layer_outputs.append(x.clone())
     xn = rmsnorm(x, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
     logits = xn @ head.T

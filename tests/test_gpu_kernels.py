@@ -35,6 +35,16 @@ def test_gemm_simple(M, N, K, xd, wd, yd):
     assert rel(out, ref) < (1e-5 if yd == torch.float32 else 6e-3)
 
 
+def test_gemm_simple_sums_twelve_thousand_terms_in_float32():
+    """The float32 path's product at the longest reduction of the model shapes (a feed-forward of 12,288) against
+    float64."""
+    from purhie_b200.csrc import ops
+    x, w = rnd(5, 12288, seed=21), rnd(130, 12288, seed=22)
+    out = torch.full((5, 130), float("nan"), device=DEV)
+    ops.gemm_simple(x, w, out)
+    assert rel(out, x.double() @ w.double().T) < 1e-5
+
+
 def test_gemm_simple_rows_do_not_depend_on_the_batch():
     from purhie_b200.csrc import ops
     x, w = rnd(150, 200, seed=3), rnd(90, 200, seed=4)
@@ -415,6 +425,16 @@ def test_attention_generic(HQ, HKV, D, page_size, window, dtype):
     assert rel(out.cpu(), ref) < (2e-6 if dtype == torch.float32 else 8e-3)
 
 
+def test_attention_generic_float32_over_2500_keys():
+    """The float32 path's attention at a context of the length the real-size tests decode at, against float64."""
+    HQ, HKV, D, ps = 8, 2, 128, 16
+    case = paged_case([(2500, 1), (2500, 3), (2437, 1)], HQ, HKV, D, ps, torch.float32, seed=5)
+    scale = 1.0 / math.sqrt(D)
+    for window in (None, 2048):
+        out = run_generic(case, HQ, HKV, D, ps, window, scale, torch.float32)
+        assert rel(out.cpu(), dense_attention(case, HQ, HKV, D, window, scale)) < 5e-6
+
+
 @pytest.mark.parametrize("HQ,HKV,D,page_size,window", [
     (8, 2, 128, 16, None), (4, 4, 64, 16, None), (6, 2, 64, 8, 40), (16, 1, 128, 64, 200), (32, 8, 128, 16, None),
     (2, 1, 128, 3, 65), (4, 2, 128, 8, 150), (3, 3, 128, 16, 77)])
@@ -482,6 +502,44 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
                 assert got.abs().max() < 4.0, (kernel, window, key_pos, ql)
             ref = dense_attention(case, HQ, HKV, D, window, scale)
             assert rel(out.cpu(), ref) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("kernel,kw", [
+    ("generic", {}), ("bulk", {"splits": 1}), ("bulk", {"splits": 3}), ("bulk", {"splits": 8}), ("cp_async", {"splits": 1}),
+    ("cp_async", {"splits": 4}), ("tc5", {"tile_splits": 1}), ("tc5", {"tile_splits": 3}), ("mma", {})])
+def test_attention_window_edge_between_two_matching_keys(kernel, kw):
+    """Two keys match the query equally: the one at z - window (just outside the window, value 3) and the one at
+    z - window + 1 (just inside, value 7).  The right answer is 7; a kernel that lets the outer key in answers 5, one
+    that drops the inner key answers noise.  The edge is put inside a page, on a page's first slot and on a block's
+    first key, for a decode row, for both rows of a 2-token portion and for the first and last row of longer
+    portions (head size 128: the TMA decode kernel, the cp.async one, the tcgen05 and the mma.sync prefill kernels)."""
+    HQ, HKV, D, ps = 4, 2, 128, 16
+    scale = 1.0 / math.sqrt(D)
+    dtype = torch.bfloat16
+    ctx = 600
+    decode = kernel in ("bulk", "cp_async")
+    for window in (100, 88, 104, 64):            # 599 - 88 + 1 = 512 (a block's first key), 599 - 104 + 1 = 496 (a page's)
+        for ql in ((1,) if decode else (1, 2, 90, 200) if kernel == "generic" else (2, 90, 200)):
+            for which in sorted({0, ql - 1}):     # the portion's first and last row
+                case = paged_case([(ctx, ql)], HQ, HKV, D, ps, dtype, seed=4)
+                k, v = case["dense"][0]
+                z = ctx - ql + which
+                spike = torch.zeros(D, device=DEV); spike[9] = 60.0
+                case["q"][which, :] = spike.to(dtype)
+                for key_pos, value in ((z - window, 3.0), (z - window + 1, 7.0)):
+                    page, off = int(case["table"][0, key_pos // ps]), key_pos % ps
+                    case["pool"][page, 0, 0, :, off] = spike.to(dtype)
+                    case["pool"][page, 0, 1, :, off] = value
+                    k[key_pos] = spike.to(dtype)
+                    v[key_pos] = value
+                if kernel == "generic":
+                    out = run_generic(case, HQ, HKV, D, ps, window, scale, dtype)
+                else:
+                    out = run_flash(case, HQ, HKV, D, ps, window, scale, bulk=kernel != "cp_async", tc5=kernel != "mma", **kw)
+                got = out[which].float()
+                assert (got - 7.0).abs().max() < 0.05, (kernel, kw, window, ql, which, float(got.mean()))
+                ref = dense_attention(case, HQ, HKV, D, window, scale)
+                assert rel(out.cpu(), ref) < 1e-2
 
 
 # ---- per-head norm, rotation and cache write ---------------------------------------------------------------

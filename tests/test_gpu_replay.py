@@ -86,6 +86,68 @@ def test_trace_run_program(dtype, tmp_path_factory, tmp_path):
     check(got, ref, dtype, f"trace_run/{dtype}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_dumps_find_the_first_wrong_layer_by_bisection(dtype, tmp_path):
+    """``trace_run --dump-layers`` writes the residual stream after every entry of the run order.  A folder whose
+    layers 3 and 4 have changed places is replayed, a prompt whole and then its last tokens one by one; halving the
+    range of layers against the plain implementation's per-layer outputs lands on layer 3, in the prompt step and in
+    a decode step, and on no layer for the folder as it was written."""
+    import json
+    import os
+    import numpy as np
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    cfg_dict = dict(TINY["A"][0], num_hidden_layers=6)
+    good, swapped = tmp_path / "good", tmp_path / "swapped"
+    cfg = make_model(good, cfg_dict, TINY["A"][1], dtype)
+    os.makedirs(swapped)
+    tensors = {}
+    with safe_open(str(good / "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            other = name.replace("layers.3.", "layers.#.").replace("layers.4.", "layers.3.").replace("layers.#.", "layers.4.")
+            tensors[other] = f.get_tensor(name).contiguous()
+    save_file(tensors, str(swapped / "model.safetensors"))
+    (swapped / "config.json").write_text((good / "config.json").read_text())
+    toks = random_tokens(45, cfg.vocab_size, 5)
+    pc, pw = P.read_model(str(good))
+    layers = []
+    P.forward(pc, pw, toks, layer_outputs=layers)
+    L, E = cfg.num_hidden_layers, cfg.hidden_size
+    tol = 1e-4 if dtype == "float32" else 3e-2
+
+    def first_wrong(folder):
+        out = tmp_path / f"out_{folder.name}"
+        tr = TraceRun(folder, dtype, out, max_tokens=128, extra=["--dump-layers"])
+        try:
+            tr.step(0, [("a", toks[:40], [])])
+            for k in range(40, 45):
+                tr.step(k, [("a", toks[k:k + 1], [0])])
+        finally:
+            tr.close()
+
+        def wrong(step, rows, layer):
+            got = torch.from_numpy(np.fromfile(out / f"{step}.layer{layer}.f32", dtype="<f4").reshape(-1, E).copy())
+            return rel_err(got, layers[layer][rows]) > tol
+
+        found = []
+        for step, rows in ((0, slice(0, 40)), (44, slice(44, 45))):
+            if not wrong(step, rows, L - 1):
+                found.append(None)
+                continue
+            lo, hi = 0, L - 1                     # the first wrong layer lies in [lo, hi]
+            while lo < hi:
+                mid = (lo + hi) // 2
+                if wrong(step, rows, mid):
+                    hi = mid
+                else:
+                    lo = mid + 1
+            found.append(lo)
+        return found
+
+    assert first_wrong(good) == [None, None]
+    assert first_wrong(swapped) == [3, 3]
+
+
 def test_first_tokens_and_long_decoding(tmp_path_factory):
     """The first tokens of a sequence (positions 0, 1, 2 one by one) and 250 decoded tokens in a row."""
     from purhie_b200.engine import Engine
