@@ -114,6 +114,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the mixed step")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="run one phase only, with few launches around it (for profiling under ncu)")
+    ap.add_argument("--leave-out", default="", metavar="NAMES",
+                    help="with --phase decode: launchers (comma separated, e.g. add_rmsnorm,decode_bulk) that the timed steps "
+                         "skip; the difference to a run without shows what they cost inside the graph (no benchmark value)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -158,8 +161,14 @@ def main():
     else:
         for _ in range(3 if args.phase == "all" else 1):
             prefill_once()
+        from purhie_b200 import native as _native
+        if _native.profile_enabled():
+            _native.profile_report(True)             # the warm-up runs do not count
         prefill_ms = median([prefill_once() for _ in range(5 if args.phase == "all" else 1)])
     if args.phase == "prefill":
+        from purhie_b200 import native
+        if native.profile_enabled():
+            sys.stderr.write(native.format_profile(native.profile_report(), f"prefill of {PREFILL_TOKENS} tokens, {args.layers} layers") + "\n")
         print(json.dumps({"phase": "prefill", "ms": prefill_ms, "layers": args.layers}))
         return 0
     T, E, FF, V = PREFILL_TOKENS, cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
@@ -186,6 +195,15 @@ def main():
         bytes_step = weight_bytes + batch * (ctx0 + steps / 2.0) * kv_bytes_per_token
         return ms, launches, bytes_step
 
+    if args.leave_out:
+        if args.phase != "decode":
+            print("bench.py: --leave-out goes with --phase decode")
+            return 2
+        from purhie_b200 import native
+        native.lib().qe_profile_leave_out(args.leave_out.encode())     # the graphs are captured after this
+    from purhie_b200 import native as _native
+    if _native.profile_enabled():
+        _native.profile_report(True)                 # what came before the timed steps does not count
     sampler = ClockSampler()
     sampler.start()
     ms_step, launches, bytes_step = decode_run(args.batch, args.steps, args.warmup)
@@ -211,7 +229,11 @@ def main():
             mixed_once()
         points[f"mixed_b{n_dec}_chunk{chunk}_ms"] = round(median([mixed_once() for _ in range(5)]), 3)
     if args.phase == "decode":
-        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": ms_step, "layers": args.layers}))
+        from purhie_b200 import native
+        if native.profile_enabled():             # PURHIE_PROFILE=1: every launch between events, graphs off
+            sys.stderr.write(native.format_profile(native.profile_report(), f"decode, batch {args.batch}, {args.layers} layers") + "\n")
+        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": ms_step, "layers": args.layers,
+                          "left_out": args.leave_out or None}))
         return 0
 
     # ---- end to end through the Python entry point ------------------------------------------------------
