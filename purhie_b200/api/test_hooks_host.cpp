@@ -28,7 +28,7 @@ std::vector<CacheNeed> needs_from_json(const Json& list) {
     std::vector<CacheNeed> needs;
     for (const Json& n : list.items()) {
         const std::string kind = n.get_string("kind", "none");
-        if (kind == "pages") needs.push_back(CacheNeed::pages((int)n.at("kv_heads").as_int(), (int)n.at("head_dim").as_int(), (int)n.get_int("window", 0)));
+        if (kind == "pages") needs.push_back(CacheNeed::pages((int)n.at("kv_heads").as_int(), (int)n.at("head_dim").as_int(), (int)n.get_int("window", 0), (int)n.get_int("value_dim", 0)));
         else if (kind == "state") {
             std::vector<int64_t> shape;
             for (const Json& d : n.at("shape").items()) shape.push_back(d.as_int());
@@ -55,6 +55,8 @@ Json cache_info(const CacheManager& c) {
         gj.set("window", g.window ? Json(g.window) : Json());
         gj.set("kv_heads", g.kv_heads);
         gj.set("head_dim", g.head_dim);
+        gj.set("value_dim", g.value_dim);
+        gj.set("page_stride", (long long)g.page_stride);
         gj.set("used", g.allocator.num_pages() - g.allocator.num_free());
         groups.push(gj);
     }

@@ -50,12 +50,13 @@ class CacheNeed:
     head_dim: int = 0
     window: Optional[int] = None          # pages: None keeps all keys, W keeps the last W positions
     state_shape: Tuple[int, ...] = ()
+    value_dim: int = 0                    # pages: width of a value row where it differs from a key row's (0: head_dim)
 
     @staticmethod
-    def pages(kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
+    def pages(kv_heads: int, head_dim: int, window: Optional[int] = None, value_dim: int = 0) -> "CacheNeed":
         if window is not None and window < 1:
             raise ValueError("a window must hold at least one position")
-        return CacheNeed("pages", kv_heads, head_dim, window)
+        return CacheNeed("pages", kv_heads, head_dim, window, value_dim=0 if value_dim == head_dim else value_dim)
 
     @staticmethod
     def state(shape: Sequence[int]) -> "CacheNeed":
@@ -63,7 +64,8 @@ class CacheNeed:
 
     def to_json(self) -> dict:
         if self.kind == "pages":
-            return {"kind": "pages", "kv_heads": self.kv_heads, "head_dim": self.head_dim, "window": self.window or 0}
+            return {"kind": "pages", "kv_heads": self.kv_heads, "head_dim": self.head_dim, "window": self.window or 0,
+                    "value_dim": self.value_dim}
         if self.kind == "state":
             return {"kind": "state", "shape": list(self.state_shape)}
         return {"kind": "none"}

@@ -90,11 +90,11 @@ CacheManager::CacheManager(std::vector<CacheNeed> needs, int page_size, std::vec
         if (need.kind != CacheNeed::Pages) continue;
         int gi = -1;
         for (const PageGroup& g : groups_)
-            if (g.kv_heads == need.kv_heads && g.head_dim == need.head_dim && g.window == need.window) gi = g.index;
+            if (g.kv_heads == need.kv_heads && g.head_dim == need.head_dim && g.value_dim == need.v_dim() && g.window == need.window) gi = g.index;
         if (gi < 0) {
             PageGroup g;
             g.index = gi = (int)groups_.size();
-            g.kv_heads = need.kv_heads; g.head_dim = need.head_dim; g.window = need.window;
+            g.kv_heads = need.kv_heads; g.head_dim = need.head_dim; g.value_dim = need.v_dim(); g.window = need.window;
             groups_.push_back(std::move(g));
         }
         groups_[gi].entries.push_back(i);
@@ -105,7 +105,7 @@ CacheManager::CacheManager(std::vector<CacheNeed> needs, int page_size, std::vec
         throw Error(kInvalidArg, std::to_string(num_pages.size()) + " page counts for " + std::to_string(groups_.size()) + " groups");
     for (size_t i = 0; i < groups_.size(); i++) {
         groups_[i].allocator = PageAllocator(num_pages[i]);
-        groups_[i].page_stride = (long long)groups_[i].entries.size() * 2 * groups_[i].kv_heads * page_size_ * groups_[i].head_dim;
+        groups_[i].page_stride = (long long)groups_[i].entries.size() * groups_[i].kv_heads * page_size_ * (groups_[i].head_dim + groups_[i].value_dim);
     }
 }
 
@@ -304,11 +304,13 @@ CacheView CacheManager::view(int entry, int owner) const {
         const PageGroup& g = groups_[entry_group(owner)];
         const int slot = g.entry_slot(owner);
         const size_t elem = dtype_size(dtype_);
-        const size_t kv = (size_t)g.kv_heads * page_size_ * g.head_dim;         // elements of one K (or V) block
+        const size_t k_elems = (size_t)g.kv_heads * page_size_ * g.head_dim;    // elements of the entry's keys in a page
+        const size_t v_elems = (size_t)g.kv_heads * page_size_ * g.value_dim;   // ... and of its values
         char* base = static_cast<char*>(g.pool.data());
         v.group = g.index;
-        v.k_base = base + ((size_t)slot * 2 * kv) * elem;
-        v.v_base = base + ((size_t)slot * 2 * kv + kv) * elem;
+        v.k_base = base + ((size_t)slot * (k_elems + v_elems)) * elem;
+        v.v_base = base + ((size_t)slot * (k_elems + v_elems) + k_elems) * elem;
+        v.kv_heads = g.kv_heads; v.key_dim = g.head_dim; v.value_dim = g.value_dim;
         v.kv_dtype = dtype_;
         v.page_stride = g.page_stride;
         v.page_size = page_size_;

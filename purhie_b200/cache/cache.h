@@ -11,7 +11,8 @@
 // is admitted.  The reference itself keeps one cache per sequence, made of blocks of 256 positions that are never
 // given back before the sequence is freed (src/kv_cache.cpp:133-226, 242-260; src/inference.cpp:1784-1802).
 //
-// A page of a group is laid out [entry][K|V][kv_head][token in page][head_dim].
+// A page of a group is laid out [entry][K|V][kv_head][token in page][head_dim] (the V part value_dim wide where a
+// mixer's values are not as wide as its keys).
 // The bookkeeping touches no device until materialize(), so it is tested without one.
 #pragma once
 
@@ -58,10 +59,10 @@ private:
 
 struct PageGroup {
     int index = 0;
-    int kv_heads = 0, head_dim = 0, window = 0;
+    int kv_heads = 0, head_dim = 0, value_dim = 0, window = 0;      // value_dim: as CacheNeed::v_dim()
     std::vector<int> entries;                      // run-order entries whose keys and values live in this group
     PageAllocator allocator;
-    DeviceBuffer pool;                             // [pages, entries, 2, kv_heads, page_size, head_dim]
+    DeviceBuffer pool;                             // [pages, entries, {K: kv_heads x page_size x head_dim, V: ... x value_dim}]
     long long page_stride = 0;                     // elements per page
     int entry_slot(int entry) const;
 };

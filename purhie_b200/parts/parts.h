@@ -71,12 +71,17 @@ public:
 struct CacheNeed {
     enum Kind { None, Pages, State } kind = None;
     int kv_heads = 0, head_dim = 0;
+    int value_dim = 0;                            // pages: width of a value row when it differs from a key row's (0: head_dim)
     int window = 0;                               // pages: 0 keeps all keys, W keeps the last W positions
+    int v_dim() const { return value_dim > 0 ? value_dim : head_dim; }
     std::vector<int64_t> state_shape;             // state: shape of one request's state
     DType state_dtype = DType::F32;
-    static CacheNeed pages(int kv_heads, int head_dim, int window = 0) {
+    static CacheNeed pages(int kv_heads, int head_dim, int window = 0, int value_dim = 0) {
         if (window < 0) throw Error(kInvalidArg, "a window must hold at least one position");
-        CacheNeed n; n.kind = Pages; n.kv_heads = kv_heads; n.head_dim = head_dim; n.window = window; return n;
+        if (kv_heads < 1 || head_dim < 1 || value_dim < 0) throw Error(kInvalidArg, "a page holds at least one head of at least one element");
+        CacheNeed n; n.kind = Pages; n.kv_heads = kv_heads; n.head_dim = head_dim; n.window = window;
+        n.value_dim = value_dim == head_dim ? 0 : value_dim;
+        return n;
     }
     static CacheNeed state(std::vector<int64_t> shape, DType dtype = DType::F32) {
         CacheNeed n; n.kind = State; n.state_shape = std::move(shape); n.state_dtype = dtype; return n;
@@ -131,6 +136,7 @@ struct CacheView {
     int group = -1;
     void* k_base = nullptr;                  // K (V) of this entry in page 0; pages are page_stride elements apart
     void* v_base = nullptr;
+    int kv_heads = 0, key_dim = 0, value_dim = 0;   // a page holds [kv_heads][page_size][key_dim] keys, then the values likewise
     DType kv_dtype = DType::F32;
     long long page_stride = 0;
     int page_size = 0;
