@@ -178,6 +178,7 @@ API const char* qe_part_cache_need(void* h) {
         j.set("kind", n.kind == CacheNeed::Pages ? "pages" : n.kind == CacheNeed::State ? "state" : "none");
         j.set("kv_heads", n.kv_heads);
         j.set("head_dim", n.head_dim);
+        if (n.kind == CacheNeed::Pages && n.value_dim) j.set("value_dim", n.value_dim);
         j.set("window", n.window ? Json(n.window) : Json());
         Json shape = Json::array();
         for (auto d : n.state_shape) shape.push((long long)d);

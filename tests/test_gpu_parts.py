@@ -188,6 +188,38 @@ def test_toy_parts_alone_against_torch(toys, tmp_path):
     assert t.shape == (128, 16) and abs(t[100, 3] - math.cos(100 * 1e4 ** (-6 / 16) / 4.0)) < 1e-6
 
 
+def test_toy_mixer_keeps_values_narrower_than_its_keys_in_pages(toys, tmp_path):
+    """A mixer from the plugin that states keys of 12 and values of 5 elements: the cache manager gives it pages of
+    that shape, and stepping it in portions and one token at a time, two requests side by side over pages that are
+    handed out in turn, gives what causal attention over the whole sequences gives."""
+    from purhie_b200.parts import PartProbe
+    E, DK, DV = 20, 12, 5
+    g = torch.Generator().manual_seed(4)
+    w = {n: torch.randn(*shape, generator=g) * 0.4 for n, shape in (("wq", (DK, E)), ("wk", (DK, E)), ("wv", (DV, E)), ("wo", (E, DV)))}
+    m = PartProbe("mixer", "toy_narrow_value_attention", {"hidden_size": E, "key_dim": DK, "value_dim": DV,
+                                                           "names": {n: n for n in w}})
+    m.bind_folder(folder_with(tmp_path, w, "narrow"))
+    assert m.cache_need() == {"kind": "pages", "kv_heads": 1, "head_dim": DK, "value_dim": DV, "window": None, "state_shape": []}
+    m.mixer_cache(4, 12, max_requests=2)                             # pages of 4 tokens
+
+    def ref(x):
+        x = x.double()
+        q, k, v = x @ w["wq"].double().T, x @ w["wk"].double().T, x @ w["wv"].double().T
+        s = (q @ k.T) / math.sqrt(DK)
+        s = s.masked_fill(torch.triu(torch.ones(len(x), len(x), dtype=torch.bool), 1), float("-inf"))
+        return torch.softmax(s, -1) @ v @ w["wo"].double().T
+
+    xa, xb = torch.randn(14, E, generator=g), torch.randn(9, E, generator=g)
+    m.add_request(1); m.add_request(2)
+    a0 = m.mixer_step([(1, 6)], xa[:6].numpy())
+    ba = m.mixer_step([(2, 9), (1, 3)], torch.cat([xb, xa[6:9]]).numpy())
+    a2 = [m.mixer_step([(1, 1)], xa[i:i + 1].numpy()) for i in range(9, 14)]
+    got_a = torch.from_numpy(np.concatenate([a0, ba[9:]] + a2))
+    assert rel_err(got_a, ref(xa)) < 1e-5 and rel_err(torch.from_numpy(ba[:9]), ref(xb)) < 1e-5
+    m.release(1); m.add_request(3)                                    # request 3 gets the pages request 1 gave back
+    assert rel_err(torch.from_numpy(m.mixer_step([(3, 14)], xa.numpy())), ref(xa)) < 1e-5
+
+
 def test_toy_architecture_is_registered_built_and_stepped(toys, tmp_path):
     from purhie_b200.config import load_config
     from purhie_b200.engine import Engine, StepEntry

@@ -1,5 +1,6 @@
 // Parts that the framework does not have, defined by a test and registered through the public registries when this
-// shared object is loaded: a mixer with state of its own (and step metadata of its own), another position encoding, a
+// shared object is loaded: a mixer with state of its own (and step metadata of its own), a mixer that keeps values
+// narrower than its keys in the cache manager's pages, another position encoding, a
 // feed-forward with routing, an arrangement with a third norm, and an architecture nobody has that strings them
 // together with the framework's own attention and SwiGLU.  No file of the framework changes for any of it; the only
 // header a part needs is parts/parts.h (config/config.h for an architecture).
@@ -66,6 +67,86 @@ public:
 private:
     int64_t size_;
     Tensor w_;
+};
+
+// ---- a mixer whose values are narrower than its keys ----------------------------------------------------------------
+// One head: keys of key_dim, values of value_dim < key_dim (a "compressed" value), both kept in the cache manager's
+// pages: the mixer states the two widths in its CacheNeed and gets pages laid out [K: page_size x key_dim][V: page_size
+// x value_dim].  Plain causal attention over the request's pages, float32.
+__global__ void narrow_write_kernel(const float* k, const float* v, const int32_t* slot_mapping, float* k_base, float* v_base,
+                                    long long page_stride, int page_size, int Dk, int Dv) {
+    const int t = blockIdx.x;
+    const int slot = slot_mapping[t], page = slot / page_size, off = slot % page_size;
+    for (int d = threadIdx.x; d < Dk; d += blockDim.x) k_base[(size_t)page * page_stride + (size_t)off * Dk + d] = k[(size_t)t * Dk + d];
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) v_base[(size_t)page * page_stride + (size_t)off * Dv + d] = v[(size_t)t * Dv + d];
+}
+__global__ void narrow_attend_kernel(const float* q, const int32_t* row_seg, const int32_t* positions, const int32_t* block_table,
+                                     int table_width, const float* k_base, const float* v_base, long long page_stride,
+                                     int page_size, int Dk, int Dv, float* out) {
+    extern __shared__ float score[];                      // one per visible key
+    __shared__ float red[2];
+    const int t = blockIdx.x, z = positions[t];
+    const int32_t* table = block_table + (size_t)row_seg[t] * table_width;
+    for (int p = threadIdx.x; p <= z; p += blockDim.x) {
+        const float* kp = k_base + (size_t)table[p / page_size] * page_stride + (size_t)(p % page_size) * Dk;
+        float s = 0.0f;
+        for (int d = 0; d < Dk; d++) s += q[(size_t)t * Dk + d] * kp[d];
+        score[p] = s * rsqrtf((float)Dk);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = -INFINITY, l = 0.0f;
+        for (int p = 0; p <= z; p++) m = fmaxf(m, score[p]);
+        for (int p = 0; p <= z; p++) l += expf(score[p] - m);
+        red[0] = m; red[1] = l;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int p = 0; p <= z; p++)
+            acc += expf(score[p] - red[0]) * v_base[(size_t)table[p / page_size] * page_stride + (size_t)(p % page_size) * Dv + d];
+        out[(size_t)t * Dv + d] = acc / red[1];
+    }
+}
+
+class NarrowValueAttention : public Mixer {
+public:
+    NarrowValueAttention(const Json& p, BuildContext& b)
+        : Mixer(p, b), size_(p.at("hidden_size").as_int()), dk_((int)p.at("key_dim").as_int()), dv_((int)p.at("value_dim").as_int()) {}
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("wq"), {dk_, size_}, Role::Matrix, Init::Normal}, {name_of("wk"), {dk_, size_}, Role::Matrix, Init::Normal},
+                {name_of("wv"), {dv_, size_}, Role::Matrix, Init::Normal}, {name_of("wo"), {size_, dv_}, Role::Matrix, Init::Normal}};
+    }
+    void bind(WeightSource& src) override {
+        wq_ = src.fetch(name_of("wq")); wk_ = src.fetch(name_of("wk")); wv_ = src.fetch(name_of("wv")); wo_ = src.fetch(name_of("wo"));
+    }
+    CacheNeed cache_need() const override { return CacheNeed::pages(1, dk_, 0, dv_); }
+    Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
+        if (cache.kv_dtype != DType::F32 || x.dtype != DType::F32) throw Error(kInvalidState, "the toy attention runs in float32");
+        if (cache.key_dim != dk_ || cache.value_dim != dv_ || cache.kv_heads != 1) throw Error(kInvalidState, "the cache is not laid out for this mixer");
+        const CoreKernels& kn = core_kernels();
+        const GroupStep& g = ctx.groups.at(cache.group);
+        Workspace& ws = *ctx.workspace;
+        auto product = [&](const Tensor& in, const Tensor& w, const char* name, int n_out) {
+            Tensor out = ws.get(name, {ctx.T, n_out}, DType::F32);
+            QE_LAUNCH(kn, kn.gemm_simple(in.data, in.code(), w.data, w.code(), out.data, out.code(), ctx.T, n_out, (int)w.shape[1], ctx.stream));
+            return out;
+        };
+        Tensor q = product(x, wq_, "toy_narrow_q", dk_), k = product(x, wk_, "toy_narrow_k", dk_), v = product(x, wv_, "toy_narrow_v", dv_);
+        narrow_write_kernel<<<ctx.T, 32, 0, ctx.stream>>>(k.as<float>(), v.as<float>(), g.slot_mapping, (float*)cache.k_base,
+                                                          (float*)cache.v_base, cache.page_stride, cache.page_size, dk_, dv_);
+        int longest = 1;
+        for (int c : ctx.ctx_lens) longest = std::max(longest, c);
+        Tensor o = ws.get("toy_narrow_o", {ctx.T, dv_}, DType::F32);
+        narrow_attend_kernel<<<ctx.T, 64, (size_t)longest * sizeof(float), ctx.stream>>>(
+            q.as<float>(), ctx.row_seg, ctx.position_column(0), g.block_table, g.table_width, (const float*)cache.k_base,
+            (const float*)cache.v_base, cache.page_stride, cache.page_size, dk_, dv_, o.as<float>());
+        return Addend(product(o, wo_, "toy_narrow_y", (int)size_), 1);
+    }
+private:
+    int64_t size_;
+    int dk_, dv_;
+    Tensor wq_, wk_, wv_, wo_;
 };
 
 // ---- another position encoding --------------------------------------------------------------------------------------
@@ -279,6 +360,7 @@ public:
 extern "C" __attribute__((visibility("default"))) int qe_plugin_init(void) {
     try {
         register_part("mixer", "toy_running_mean", [](const Json& p, BuildContext& b) { return std::make_shared<RunningMeanMixer>(p, b); });
+        register_part("mixer", "toy_narrow_value_attention", [](const Json& p, BuildContext& b) { return std::make_shared<NarrowValueAttention>(p, b); });
         register_part("position", "toy_scaled_rope", [](const Json& p, BuildContext& b) { return std::make_shared<ScaledRotary>(p, b); });
         register_part("feed_forward", "toy_top1", [](const Json& p, BuildContext& b) { return std::make_shared<Top1Routed>(p, b); });
         register_arrangement("toy_sandwich", [](const LayerSpec& l, BuildContext& b) { return std::unique_ptr<Arrangement>(new SandwichBlock(l, b)); });
@@ -291,6 +373,7 @@ extern "C" __attribute__((visibility("default"))) int qe_plugin_init(void) {
 
 extern "C" __attribute__((visibility("default"))) int qe_plugin_exit(void) {
     unregister_part("mixer", "toy_running_mean");
+    unregister_part("mixer", "toy_narrow_value_attention");
     unregister_part("position", "toy_scaled_rope");
     unregister_part("feed_forward", "toy_top1");
     unregister_arrangement("toy_sandwich");
