@@ -465,7 +465,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int a = a0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             const size_t split_off = (size_t)split * (size_t)p.split_stride;
-            constexpr int CH = BN >= 32 ? 32 : 16;
+            constexpr int CH = BN > 64 ? 32 : 16;         // chunks of 16 keep the few-token kernels at registers that let a neighbour start beside them
 #pragma unroll 1
             for (int c = 0; c < BN; c += CH) {
                 uint32_t r[CH];
