@@ -152,6 +152,50 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
     }
 }
 
+// The same sum with the norm's weight but without the row's factor: v = x + addends (stored back), y = v * weight in the
+// output type, and the sum of v^2 over this CTA's chunk of the row in sumsq[row][chunk].  Whoever consumes y applies
+// rsqrt(sum over the chunks / E + eps) itself (a product's epilogue, the per-head norm behind the qkv product: the
+// factor is one number per row and commutes with the product).  A row is spread over ceil(E / 512) CTAs of 128 threads
+// instead of sitting in one, which is what this form is for: few rows, many addends.
+constexpr int SUMSQ_CHUNK = 512;
+
+template <typename TA, typename TY>
+__global__ void __launch_bounds__(128)
+add_weight_sumsq_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits, long long add_split_stride,
+                        const float* __restrict__ weight, int E, TY* __restrict__ y, float* __restrict__ sumsq) {
+    __shared__ float part[4];
+    pdl_launch_dependents();
+    const int r = blockIdx.x, chunk = blockIdx.y;
+    const int i = chunk * SUMSQ_CHUNK + threadIdx.x * 4;
+    const float4 w = i < E ? Vec4<float>::load(weight + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    pdl_wait();
+    float ss = 0.0f;
+    if (i < E) {
+        float* xr = x + (size_t)r * E + i;
+        float4 acc = Vec4<float>::load(xr);
+        if (add) {
+            const TA* a = add + (size_t)r * E + i;
+            for (int s0 = 0; s0 < add_splits; s0 += MANY_PARTS_IN_FLIGHT) {       // loads in flight, added in order
+                float4 u[MANY_PARTS_IN_FLIGHT];
+#pragma unroll
+                for (int j = 0; j < MANY_PARTS_IN_FLIGHT; ++j)
+                    u[j] = s0 + j < add_splits ? Vec4<TA>::load(a + (size_t)(s0 + j) * add_split_stride)
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int j = 0; j < MANY_PARTS_IN_FLIGHT; ++j)
+                    if (s0 + j < add_splits) { acc.x += u[j].x; acc.y += u[j].y; acc.z += u[j].z; acc.w += u[j].w; }
+            }
+            Vec4<float>::store(xr, acc);
+        }
+        Vec4<TY>::store(y + (size_t)r * E + i, make_float4(acc.x * w.x, acc.y * w.y, acc.z * w.z, acc.w * w.w));
+        ss = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) sumsq[(size_t)r * gridDim.y + chunk] = ((part[0] + part[1]) + part[2]) + part[3];
+}
+
 // SwiGLU over rows laid out [g0, u0, g1, u1, ...] (gate and up rows of the weight interleaved, so that a tile of
 // the product holds matching pairs): out[t, j] = silu(g_j) * u_j.  Four outputs per thread when FF % 4 == 0.
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
@@ -262,6 +306,28 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
     PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, LAUNCH(TA, TY)));
 #undef LAUNCH
     return check_launch("add_rmsnorm");
+}
+
+// x [n_rows, E] float32 += the addends (add_splits partial sums, or none); y = x * weight without the row's factor;
+// sumsq [n_rows, chunks] with chunks = ceil(E / 512): the row's sum of squares in parts.  E a multiple of 4 and every
+// pointer 16-byte aligned (8 for bfloat16), else refused.
+PH_EXPORT int ph_add_weight_sumsq(float* x, const void* add, int add_dtype, int add_splits, long long add_split_stride,
+                                  const float* weight, int n_rows, int E, void* y, int y_dtype, float* sumsq, int chunks,
+                                  cudaStream_t stream) {
+    if (!x || !weight || !y || !sumsq || n_rows < 0 || E < 1 || !valid_dtype(add_dtype) || !valid_dtype(y_dtype) ||
+        (add && add_splits < 1))
+        return fail(PH_ERR_ARG, "add_weight_sumsq: bad arguments (rows %d, E %d)", n_rows, E);
+    if (chunks != (E + SUMSQ_CHUNK - 1) / SUMSQ_CHUNK)
+        return fail(PH_ERR_ARG, "add_weight_sumsq: a row of %d elements has %d chunks, not %d", E, (E + SUMSQ_CHUNK - 1) / SUMSQ_CHUNK, chunks);
+    if (E % 4 || (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)y | (uintptr_t)add) & 15) || (add && add_split_stride % 4))
+        return fail(PH_ERR_UNSUPPORTED, "add_weight_sumsq: rows must be a multiple of 4 elements and 16-byte aligned");
+    if (n_rows == 0) return PH_OK;
+#define LAUNCH_SUMSQ(TA, TY)                                                                                          \
+    launch_overlapped(add_weight_sumsq_kernel<TA, TY>, dim3(n_rows, chunks), dim3(128), 0, stream, x, (const TA*)add, \
+                      add_splits, add_split_stride, weight, E, (TY*)y, sumsq)
+    PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, LAUNCH_SUMSQ(TA, TY)));
+#undef LAUNCH_SUMSQ
+    return check_launch("add_weight_sumsq");
 }
 
 PH_EXPORT int ph_swiglu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out,

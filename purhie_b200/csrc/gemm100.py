@@ -8,7 +8,7 @@ chooses among these in parts/linear.cpp.
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_void_p
+from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
 import torch
@@ -18,7 +18,7 @@ from .ops import KernelError, call, register_signatures
 
 register_signatures("gemm100", {
     "ph_gemm_bf16_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_void_p, c_void_p],
+                             c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p],
     "ph_gemm_bf16_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p, c_void_p],
 })
@@ -64,10 +64,12 @@ def sm_count(device) -> int:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, block_n: int, splits: int = 1,
-         max_ctas: int = 0, swiglu: bool = False, accumulate: bool = False) -> torch.Tensor:
+         max_ctas: int = 0, swiglu: bool = False, accumulate: bool = False, row_sumsq: Optional[torch.Tensor] = None,
+         row_width: int = 0, row_eps: float = 0.0) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (out [splits, M, N] float32 partial sums when splits > 1).  With
     ``swiglu`` the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up.  ``accumulate``
-    (plain orientation, float32, one split): out += the product."""
+    (plain orientation, float32, one split): out += the product.  ``row_sumsq`` [M, chunks] (swapped, bfloat16 out):
+    the rows of x lack the factor rsqrt(sum(row_sumsq[m]) / row_width + row_eps); the epilogue applies it."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"gemm_tcgen05: {name} must be a contiguous bfloat16 CUDA tensor")
@@ -77,7 +79,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
         raise KernelError(f"gemm_tcgen05: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     call("gemm100", "ph_gemm_bf16_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), ops._code(out.dtype), M, N, K,
          1 if swapped else 0, block_n, splits, max_ctas, 1 if swiglu else 0, 1 if accumulate else 0,
-         error_flag(x.device).data_ptr(), ops._stream())
+         None if row_sumsq is None else row_sumsq.data_ptr(), 0 if row_sumsq is None else row_sumsq.shape[-1], row_width,
+         float(row_eps), error_flag(x.device).data_ptr(), ops._stream())
     return out
 
 

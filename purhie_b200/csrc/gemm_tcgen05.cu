@@ -52,6 +52,12 @@ struct GemmParams {
     int swiglu;          // 1: columns are (gate, up) pairs; out[a, j] = silu(D[a, 2j]) * D[a, 2j + 1] (plain orientation)
     long long ld;        // row length of out
     long long split_stride;
+    // Swapped orientation with bfloat16 output: a factor per token that the norm in front left out of the activations,
+    // rsqrt(sum over the chunks of row_sumsq[token][chunk] / row_width + row_eps), applied to the accumulator before
+    // anything else happens to it (the product is linear in its rows).  Null: none.
+    const float* row_sumsq;
+    int row_chunks, row_width;
+    float row_eps;
     int* error_flag;
 };
 
@@ -294,10 +300,15 @@ __device__ __forceinline__ void store_chunk_swapped_swiglu(const GemmParams& p, 
 // instead of one 2-byte store per value.  With the activation, gate and up features are neighbouring lanes: the
 // even lane works out token j, the odd lane token j + 1 of every pair of tokens, after one exchange.
 // a_base: the warp's first output feature; every lane of the warp calls this.
+// factor: lane (c + l) % 32 holds the factor of token b0 + c + l (1 where the norm left none out).
 template <int CH>
-__device__ __forceinline__ void store_chunk_swapped_bf16(const GemmParams& p, const uint32_t* r, __nv_bfloat16* buf, int a_base,
-                                                         int lane, int b0, int c) {
+__device__ __forceinline__ void store_chunk_swapped_bf16(const GemmParams& p, uint32_t* r, __nv_bfloat16* buf, int a_base,
+                                                         int lane, int b0, int c, float factor) {
     const int W = p.swiglu ? 16 : 32;                 // output columns of this warp
+    if (p.row_sumsq) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * __shfl_sync(0xffffffffu, factor, (c + j) & 31));
+    }
     if (p.swiglu) {
         const int odd = lane & 1;
 #pragma unroll
@@ -460,18 +471,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int w = blockIdx.x; w < work_total && ok; w += gridDim.x) {
             const int split = w % p.splits, tile = w / p.splits;
             const int a0 = (tile % p.a_tiles) * BM, b0 = (tile / p.a_tiles) * BN;
+            constexpr int CH = BN > 64 ? 32 : 16;         // chunks of 16 keep the few-token kernels at registers that let a neighbour start beside them
+            // the factors of this item's tokens (register i, lane l: token b0 + 32 i + l), fetched while the products run
+            constexpr int FR = BN > 32 ? BN / 32 : 1;
+            float factor[FR];
+#pragma unroll
+            for (int i = 0; i < FR; ++i) {
+                factor[i] = 1.0f;
+                const int t = b0 + i * 32 + lane;
+                if (p.row_sumsq && i * 32 + lane < BN && t < p.rows_b) {
+                    float s = 0.0f;
+                    for (int k = 0; k < p.row_chunks; ++k) s += p.row_sumsq[(size_t)t * p.row_chunks + k];
+                    factor[i] = rsqrtf(s / (float)p.row_width + p.row_eps);
+                }
+            }
             if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
             tc_fence_after();
             const int a = a0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             const size_t split_off = (size_t)split * (size_t)p.split_stride;
-            constexpr int CH = BN > 64 ? 32 : 16;         // chunks of 16 keep the few-token kernels at registers that let a neighbour start beside them
 #pragma unroll 1
             for (int c = 0; c < BN; c += CH) {
                 uint32_t r[CH];
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
-                if (p.swapped && p.out_bf16) store_chunk_swapped_bf16<CH>(p, r, staging + q * 32 * 32, a0 + q * 32, lane, b0, c);
+                if (p.swapped && p.out_bf16) {
+                    float f = factor[0];                  // the register that holds this chunk's tokens, picked without an index
+#pragma unroll
+                    for (int i = 1; i < FR; ++i) if ((c >> 5) == i) f = factor[i];
+                    store_chunk_swapped_bf16<CH>(p, r, staging + q * 32 * 32, a0 + q * 32, lane, b0, c, f);
+                }
                 else if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
                 else store_chunk<CH>(p, r, a, b0, c, split_off);
             }
@@ -816,6 +845,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     p.a_tiles = 0; p.b_tiles = 0; p.splits = splits; p.kblocks = kblocks;
     p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
+    p.row_sumsq = nullptr; p.row_chunks = 0; p.row_width = 0; p.row_eps = 0.0f;
     return launch_pair(ma, mb, p, max_clusters, stream);
 }
 
@@ -824,8 +854,11 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
 // swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue
 // (the formula of src/gpu_ops.hip:103-114 in the reference).
 // accumulate: out (float32, plain orientation, one split, no activation) += the product.
+// row_sumsq [M][row_chunks] (or null), row_width, row_eps: the activations lack a factor per token, see GemmParams;
+// taken by the swapped orientation with bfloat16 output only.
 PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
                                    int swapped, int block_n, int splits, int max_ctas, int swiglu, int accumulate,
+                                   const float* row_sumsq, int row_chunks, int row_width, float row_eps,
                                    int* error_flag, cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05: bad arguments (M %d, N %d, K %d)", M, N, K);
@@ -837,6 +870,8 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     if (swiglu && (splits > 1 || (N & 1) || (!swapped && block_n < 32)))
         return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs one split, an even N and, in the plain orientation, "
                                 "tiles of 32 features or more");
+    if (row_sumsq && (!swapped || out_dtype != PH_BF16 || splits > 1 || row_chunks < 1 || row_width < 1))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: a factor per token goes with the swapped orientation, bfloat16 output and one split");
     if (accumulate && (swapped || swiglu || splits > 1 || out_dtype != PH_F32))
         return fail(PH_ERR_ARG, "gemm_tcgen05: adding into the output needs the plain orientation, float32, one split and no activation");
     const void* a = swapped ? w : x;
@@ -851,6 +886,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.splits = splits; p.kblocks = kblocks;
     p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
+    p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     switch (block_n) {
         case 16: return launch<16>(ma, mb, p, max_ctas, stream);
         case 32: return launch<32>(ma, mb, p, max_ctas, stream);

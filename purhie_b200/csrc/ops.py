@@ -99,7 +99,10 @@ _SIGNATURES = {
         "ph_cast": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
         "ph_qk_norm_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
                                      c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                     c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                     c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                     c_float, c_void_p],
+        "ph_add_weight_sumsq": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_int, c_void_p],
         "ph_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_void_p],
@@ -188,6 +191,24 @@ def add_rmsnorm(x: torch.Tensor, add: Optional[torch.Tensor], weight: Optional[t
     return out
 
 
+def add_weight_sumsq(x: torch.Tensor, add: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                     add_splits: int = 1) -> torch.Tensor:
+    """x [T, E] float32 += the addends; out = x * weight WITHOUT the row's factor; returns sumsq [T, ceil(E / 512)]
+    float32, the row's sum of squares in parts: the consumer applies rsqrt(sum / E + eps) (see elementwise.cu)."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    E = x.shape[-1]
+    T = x.numel() // E
+    chunks = -(-E // 512)
+    sumsq = torch.empty(T, chunks, dtype=torch.float32, device=x.device)
+    if add is not None:
+        _need(add, "add")
+        if add.numel() != add_splits * T * E:
+            raise KernelError(f"add_weight_sumsq: add has {add.numel()} elements, expected {add_splits} x {T} x {E}")
+    call("core", "ph_add_weight_sumsq", _ptr(x), _ptr(add), _code(add.dtype) if add is not None else F32, add_splits, T * E,
+         _ptr(weight), T, E, _ptr(out), _code(out.dtype), _ptr(sumsq), chunks, _stream())
+    return sumsq
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, splits: int = 1) -> torch.Tensor:
     """out[t, j] = silu(g[t, j]) * u[t, j] for gate_up rows laid out [g0, u0, g1, u1, ...]."""
     _need(gate_up, "gate_up"); _need(out, "out")
@@ -213,8 +234,10 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: tor
                           k_norm: Optional[torch.Tensor], bias: Optional[torch.Tensor],
                           cos_sin: Optional[torch.Tensor], n_rot: int, slot_mapping: Optional[torch.Tensor],
                           k_base: Optional[torch.Tensor], v_base: Optional[torch.Tensor], page_stride: int,
-                          page_size: int, splits: int = 1, interleaved: bool = False) -> torch.Tensor:
-    """Fused per-head norm, rotary encoding and cache write; see qk_norm_rope.cu.
+                          page_size: int, splits: int = 1, interleaved: bool = False,
+                          row_sumsq: Optional[torch.Tensor] = None, row_width: int = 0, row_eps: float = 0.0) -> torch.Tensor:
+    """Fused per-head norm, rotary encoding and cache write; see qk_norm_rope.cu.  ``row_sumsq`` [T, chunks]: the
+    rows of qkv lack the factor rsqrt(sum(row_sumsq[t]) / row_width + row_eps), which is applied here (add_weight_sumsq).
 
     ``k_base`` / ``v_base`` are views whose first element is the K / V of this cache entry in page 0.
     """
@@ -249,7 +272,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: tor
     call("core", "ph_qk_norm_rope_kv_write", _ptr(qkv), _code(qkv.dtype), splits, T * width, _ptr(bias), _ptr(q_norm),
          _ptr(k_norm), float(eps), _ptr(cos_sin), n_rot, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(q_out),
          _code(q_out.dtype), _ptr(k_base), _ptr(v_base), kv_code, page_stride, page_size, T, num_heads, num_kv_heads,
-         head_dim, 1 if interleaved else 0, _stream())
+         head_dim, 1 if interleaved else 0, _ptr(row_sumsq), 0 if row_sumsq is None else row_sumsq.shape[-1], row_width,
+         float(row_eps), _stream())
     return q_out
 
 

@@ -19,6 +19,20 @@ namespace {
 using namespace ph;
 
 constexpr int WARPS = 4;
+
+// A factor per token that the norm in front of the qkv product left out: rsqrt(sum over the chunks of sumsq[t][chunk] /
+// width + eps).  The product is linear, so the factor is applied to its result here (before the bias).  sumsq null: 1.
+struct RowFactor {
+    const float* sumsq;
+    int chunks, width;
+    float eps;
+};
+__device__ __forceinline__ float row_factor(const RowFactor& rf, int t) {
+    if (!rf.sumsq) return 1.0f;
+    float s = 0.0f;
+    for (int k = 0; k < rf.chunks; ++k) s += rf.sumsq[(size_t)t * rf.chunks + k];
+    return rsqrtf(s / (float)rf.width + rf.eps);
+}
 constexpr int MAX_D = 512;
 
 template <typename TI, typename TQ, typename TKV>
@@ -28,7 +42,7 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
                                     int n_rot, int max_pos, const int32_t* __restrict__ positions,
                                     const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                     TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                    int page_size, int HQ, int HKV, int D, int interleaved) {
+                                    int page_size, int HQ, int HKV, int D, int interleaved, RowFactor rf) {
     __shared__ float buf[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * WARPS + warp;
@@ -40,11 +54,13 @@ __global__ void qk_norm_rope_kernel(const TI* __restrict__ qkv, int splits, long
     const float* b = bias ? bias + (size_t)head * D : nullptr;
     const bool is_q = head < HQ, is_k = !is_q && head < HQ + HKV;
     float* row = buf[warp];
+    const float rs = row_factor(rf, t);
 
     float ss = 0.0f;
     for (int d = lane; d < D; d += 32) {
         float v = 0.0f;
         for (int s = 0; s < splits; ++s) v += to_float<TI>(src[(size_t)s * split_stride + d]);
+        v *= rs;
         if (b) v += b[d];
         row[d] = v;
         ss += v * v;
@@ -137,7 +153,7 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
                                          int max_pos, const int32_t* __restrict__ positions,
                                          const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                          TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                         int page_size, int HQ, int HKV) {
+                                         int page_size, int HQ, int HKV, RowFactor rf) {
     constexpr int D = 128;
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -160,6 +176,7 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
     const float4 gq = q_w ? ld4(q_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
     const float4 gk = k_w ? ld4(k_w + d0) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
     pdl_wait();
+    const float rs = row_factor(rf, t);
     // every head's loads are issued before any of them is used
     float4 v[HPW];
 #pragma unroll
@@ -181,7 +198,7 @@ __global__ void qk_norm_rope_d128_kernel(const TI* __restrict__ qkv, int splits,
     for (int i = 0; i < HPW; ++i) {
         const int head = head0 + i;
         if (head >= n_heads) break;
-        float4 x = v[i];
+        float4 x = make_float4(v[i].x * rs, v[i].y * rs, v[i].z * rs, v[i].w * rs);
         if (bias) {
             const float4 b = ld4(bias + (size_t)head * D + d0);
             x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
@@ -259,7 +276,7 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
                                               int max_pos, const int32_t* __restrict__ positions,
                                               const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out,
                                               TKV* __restrict__ k_base, TKV* __restrict__ v_base, long long page_stride,
-                                              int page_size, int HQ, int HKV) {
+                                              int page_size, int HQ, int HKV, RowFactor rf) {
     constexpr int D = 128;
     pdl_launch_dependents();
     pdl_wait();
@@ -269,6 +286,7 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
     const int t = blockIdx.x;
     const int n_heads = HQ + 2 * HKV;
     const int d0 = l16 * 8;
+    const float rs = row_factor(rf, t);
     F8 v[ITERS];
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
@@ -298,6 +316,8 @@ __global__ void qk_norm_rope_d128_wide_kernel(const TI* __restrict__ qkv, int sp
         const int head = head0 + 2 * i;
         const bool live = head < n_heads;                     // the shuffles below are run by every lane
         F8 x = v[i];
+        x.a = make_float4(x.a.x * rs, x.a.y * rs, x.a.z * rs, x.a.w * rs);
+        x.b = make_float4(x.b.x * rs, x.b.y * rs, x.b.z * rs, x.b.w * rs);
         if (bias && live) {
             const F8 b = ld8(bias + (size_t)head * D + d0);
             add4(x.a, b.a);
@@ -349,7 +369,8 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
                                        const float* cos_sin, int n_rot, int max_pos, const int32_t* positions,
                                        const int32_t* slot_mapping, void* q_out, int q_dtype, void* k_base,
                                        void* v_base, int kv_dtype, long long page_stride, int page_size, int T,
-                                       int HQ, int HKV, int D, int interleaved, cudaStream_t stream) {
+                                       int HQ, int HKV, int D, int interleaved, const float* row_sumsq, int row_chunks,
+                                       int row_width, float row_eps, cudaStream_t stream) {
     if (!qkv || !positions || !q_out || T < 0 || HQ < 1 || HKV < 0 || D < 2 || splits < 1 || !valid_dtype(qkv_dtype) ||
         !valid_dtype(q_dtype) || !valid_dtype(kv_dtype))
         return fail(PH_ERR_ARG, "qk_norm_rope: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
@@ -358,7 +379,9 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
         return fail(PH_ERR_ARG, "qk_norm_rope: rotary width %d must be even and at most head_dim %d", n_rot, D);
     if (slot_mapping && (!k_base || !v_base || page_size < 1))
         return fail(PH_ERR_ARG, "qk_norm_rope: a cache write needs the pool and its page size");
+    if (row_sumsq && (row_chunks < 1 || row_width < 1)) return fail(PH_ERR_ARG, "qk_norm_rope: a row factor needs its chunks and the row width");
     if (T == 0) return PH_OK;
+    const RowFactor rf = {row_sumsq, row_chunks, row_width, row_eps};
     dim3 grid(T, (HQ + 2 * HKV + WARPS - 1) / WARPS);
     const bool fast = D == 128 && (!cos_sin || (n_rot == 128 && !interleaved)) && split_stride % 4 == 0 &&
                       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)bias |
@@ -373,11 +396,11 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
         if (many)                                                                                                   \
             launch_overlapped(qk_norm_rope_d128_wide_kernel<TI, TQ, TKV, 3>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
                               splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
-                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV); \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf); \
         else                                                                                                        \
             launch_overlapped(qk_norm_rope_d128_kernel<TI, TQ, TKV, 1>, fgrid, dim3(WARPS * 32), 0, stream, (const TI*)qkv, \
                               splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions,     \
-                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV); \
+                              slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, rf); \
     } while (0)
         PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_FAST(TI, TQ, TKV))));
 #undef LAUNCH_FAST
@@ -386,7 +409,7 @@ PH_EXPORT int ph_qk_norm_rope_kv_write(const void* qkv, int qkv_dtype, int split
 #define LAUNCH(TI, TQ, TKV)                                                                                       \
     qk_norm_rope_kernel<TI, TQ, TKV><<<grid, WARPS * 32, 0, stream>>>(                                            \
         (const TI*)qkv, splits, split_stride, bias, q_norm_w, k_norm_w, eps, cos_sin, n_rot, max_pos, positions,  \
-        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, interleaved)
+        slot_mapping, (TQ*)q_out, (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, interleaved, rf)
     PH_DISPATCH(qkv_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH(TI, TQ, TKV))));
 #undef LAUNCH
     return check_launch("qk_norm_rope");

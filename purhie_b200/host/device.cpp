@@ -147,6 +147,7 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_swiglu", g_core.swiglu);
     bind(h, "core", "ph_cast", g_core.cast);
     bind(h, "core", "ph_qk_norm_rope_kv_write", g_core.qk_norm_rope_kv_write);
+    bind(h, "core", "ph_add_weight_sumsq", g_core.add_weight_sumsq);
     bind(h, "core", "ph_attention_generic", g_core.attention_generic);
     bind(h, "core", "ph_gemm_simple", g_core.gemm_simple);
     bind(h, "core", "ph_argmax", g_core.argmax);

@@ -95,7 +95,8 @@ struct CoreKernels {
     int (*cast)(const void*, int, void*, int, long long, cudaStream_t);
     int (*qk_norm_rope_kv_write)(const void*, int, int, long long, const float*, const float*, const float*, float,
                                  const float*, int, int, const int32_t*, const int32_t*, void*, int, void*, void*, int,
-                                 long long, int, int, int, int, int, int, cudaStream_t);
+                                 long long, int, int, int, int, int, int, const float*, int, int, float, cudaStream_t);
+    int (*add_weight_sumsq)(float*, const void*, int, int, long long, const float*, int, int, void*, int, float*, int, cudaStream_t);
     int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
                              const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, cudaStream_t);
     int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
@@ -120,7 +121,8 @@ struct FlashKernels {
     const char* (*last_error)(void);
 };
 struct GemmKernels {
-    int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, int*, cudaStream_t);
+    int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, const float*, int, int, float,
+                int*, cudaStream_t);
     int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int*, cudaStream_t);
     const char* (*last_error)(void);
 };

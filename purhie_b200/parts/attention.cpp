@@ -226,6 +226,13 @@ public:
         add_tiles(plan, kTileLarge, "attention.tiles128");
     }
 
+    // Few rows in bfloat16: the qkv product's float32 sums are linear in the rows, and the kernel that adds them up
+    // (per-head norm, rotation, cache write) multiplies by the factor the norm in front left out.
+    bool takes_unscaled_rows(const StepContext& ctx) const override {
+        return compute_dtype == DType::BF16 && qkv_proj_.swapped_for(ctx.T, true, false) &&
+               (!q_only_proj_.defined() || q_only_proj_.swapped_for(ctx.T, true, false));
+    }
+
     // ---- step ----------------------------------------------------------------------------------------------------
     Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
         const int T = ctx.T;
@@ -246,7 +253,8 @@ public:
             position_ ? position_->n_rot() : 0, table_.defined() ? (int)table_.shape[0] : 0, positions,
             cache.writable ? g.slot_mapping : nullptr, q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype,
             cache.page_stride, cache.page_size, T, heads_, kv_heads_written, head_dim_,
-            position_ && position_->interleaved() ? 1 : 0, ctx.stream));
+            position_ && position_->interleaved() ? 1 : 0, ctx.row_scale.sumsq, ctx.row_scale.chunks, ctx.row_scale.width,
+            ctx.row_scale.eps, ctx.stream));
         Tensor out = ws.get("attn_out", {T, q_width_}, dt);
         const int32_t* abs_positions = ctx.position_column(0);       // the mask always follows the index in the request
         if (use_flash()) {

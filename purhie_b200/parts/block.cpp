@@ -20,10 +20,18 @@ public:
     void forward(ResidualStream& stream, StepContext& ctx, const CacheView& cache) override {
         ctx.residual = stream.x.as<float>();
         ctx.residual_width = stream.x.shape[1];
-        Tensor xn = mixer_norm_->forward(stream, ctx);
+        // a consumer that applies the row's factor itself lets the norm in front leave it out (RowScale)
+        // (the option "row_factor": "norm" keeps the factor in the norm, for comparing the two forms)
+        const bool may_defer = ctx.option("row_factor") != "norm";
+        ctx.row_scale = RowScale();
+        Tensor xn = may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->forward_unscaled(stream, ctx, &ctx.row_scale)
+                                                                  : mixer_norm_->forward(stream, ctx);
         stream.add(mixer_->forward(xn, ctx, cache));
-        xn = ff_norm_->forward(stream, ctx);
+        ctx.row_scale = RowScale();
+        xn = may_defer && ff_->takes_unscaled_rows(ctx) ? ff_norm_->forward_unscaled(stream, ctx, &ctx.row_scale)
+                                                        : ff_norm_->forward(stream, ctx);
         stream.add(ff_->forward(xn, ctx));
+        ctx.row_scale = RowScale();
     }
 private:
     std::shared_ptr<Norm> mixer_norm_, ff_norm_;

@@ -41,9 +41,14 @@ public:
         return (gate_up_.fast() || down_.fast()) ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
     }
 
+    // few rows in bfloat16: the gate/up product's epilogue applies the norm's factor per row before the activation
+    bool takes_unscaled_rows(const StepContext& ctx) const override {
+        return compute_dtype == DType::BF16 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
+    }
+
     Addend forward(const Tensor& x, StepContext& ctx) override {
         const int T = ctx.T;
-        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, true);
+        Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, true, nullptr, &ctx.row_scale);
         Tensor act;
         if (gu.activated) act = gu.tensor;
         else {

@@ -82,8 +82,19 @@ std::vector<std::string> Linear::required_libraries() const {
     return fast_ ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
 }
 
+bool Linear::swapped_for(int rows, bool allow_split, bool fused_epilogue) const {
+    if (!fast_) return false;
+    const GemmPlan p = plan_gemm(rows, (int)weight_.shape[0], (int)weight_.shape[1], sm_count(), allow_split, fused_epilogue);
+    return p.swapped && !p.pair;
+}
+
+bool Linear::applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu) const {
+    // the fused activation keeps K whole and writes bfloat16 from the swapped epilogue, which is where the factor goes
+    return out_dtype == DType::BF16 && fuse_swiglu && weight_.shape[0] % 2 == 0 && swapped_for(rows, true, true);
+}
+
 Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
-                          bool allow_split, bool fuse_swiglu, float* add_into) const {
+                          bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale) const {
     const int M = rows, N = (int)weight_.shape[0], K = (int)weight_.shape[1];
     Workspace& ws = *ctx.workspace;
     const CoreKernels& core = core_kernels();
@@ -93,6 +104,9 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
         QE_LAUNCH(core, core.cast(x.data, x.code(), x32.data, x32.code(), (long long)M * K, ctx.stream));
         x = x32;
     }
+    const bool scaled = scale && scale->defined();
+    if (scaled && !(fast_ && x.dtype == DType::BF16 && applies_row_scale(M, out_dtype, fuse_swiglu)))
+        throw KernelError(label_ + ": rows without their factor reached a product that cannot apply it");
     if (!(fast_ && x.dtype == DType::BF16)) {
         Tensor out = ws.get(out_name, {M, N}, out_dtype);
         if (LaunchProfile::get().on())
@@ -111,7 +125,8 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
                                      ctx.gemm_error, ctx.stream));
         else
             QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, splits, 0, swiglu,
-                                accumulate, ctx.gemm_error, ctx.stream));
+                                accumulate, scaled ? scale->sumsq : nullptr, scaled ? scale->chunks : 0, scaled ? scale->width : 0,
+                                scaled ? scale->eps : 0.0f, ctx.gemm_error, ctx.stream));
     };
     if (fused && (p.swapped || p.splits == 1)) {
         // K stays whole, so that the epilogue holds whole sums and can apply the activation; with few tokens the

@@ -36,8 +36,15 @@ public:
     // split).  fuse_swiglu: the weight holds (gate, up) row pairs; where the kernel can, it applies the activation
     // in its epilogue and the result [rows, out / 2] comes back marked activated.  add_into (float32 [rows, out]):
     // where the kernel can add the product there in its epilogue it does, and the addend comes back empty.
+    // scale: the rows of x lack a factor per row (RowScale); only where applies_row_scale() is true, and then the
+    // kernel's epilogue multiplies by it.
     Addend operator()(const Tensor& x, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
-                      bool allow_split = false, bool fuse_swiglu = false, float* add_into = nullptr) const;
+                      bool allow_split = false, bool fuse_swiglu = false, float* add_into = nullptr,
+                      const RowScale* scale = nullptr) const;
+    // Few rows on the tensor-core kernel: the weight fills the wide side of the instruction (what plan_gemm calls
+    // swapped).  Its partial sums are linear in the rows, and its bfloat16 epilogue can apply a factor per row.
+    bool swapped_for(int rows, bool allow_split, bool fused_epilogue) const;
+    bool applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu) const;
 private:
     Tensor weight_;
     std::string label_;

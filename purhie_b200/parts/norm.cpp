@@ -27,6 +27,25 @@ public:
         return out;
     }
 
+    // The few-row form: x += addend, y = x * weight, and the row's sum of squares in chunks for the consumer to turn
+    // into the factor (bfloat16 model, rows of a multiple of four elements; else the ordinary form).
+    Tensor forward_unscaled(ResidualStream& stream, StepContext& ctx, RowScale* scale) override {
+        *scale = RowScale();
+        if (compute_dtype != DType::BF16 || size_ % 4) return forward(stream, ctx, nullptr, 0);
+        constexpr int kChunk = 512;                                   // columns per CTA of the kernel
+        const int chunks = (int)((size_ + kChunk - 1) / kChunk);
+        Tensor out = ctx.workspace->get("normed", {ctx.T, size_}, compute_dtype);
+        Tensor sumsq = ctx.workspace->get("normed_sumsq", {ctx.T, chunks}, DType::F32);
+        const CoreKernels& k = core_kernels();
+        const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
+        QE_LAUNCH(k, k.add_weight_sumsq(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
+                                        pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(), ctx.T,
+                                        (int)size_, out.data, out.code(), sumsq.as<float>(), chunks, ctx.stream));
+        stream.clear();
+        scale->sumsq = sumsq.as<float>(); scale->chunks = chunks; scale->width = (int)size_; scale->eps = (float)eps_;
+        return out;
+    }
+
 private:
     int64_t size_;
     double eps_;

@@ -159,6 +159,18 @@ struct StepArray {
     int count = 0;
 };
 
+// A normalisation whose factor per row has not been applied: the rows a norm hands out are (x * weight) and the row's
+// factor is rsqrt(sum over the chunks of sumsq[row][chunk] / width + eps).  Only a consumer that said it applies the
+// factor itself (takes_unscaled_rows) ever sees rows like that: a product is linear in its rows, so its epilogue (or
+// whoever adds up its partial sums) can multiply by the factor, and the norm's kernel needs no sum over a whole row,
+// which lets few rows be spread over many CTAs.
+struct RowScale {
+    const float* sumsq = nullptr;            // [rows, chunks] float32 on the device
+    int chunks = 0, width = 0;
+    float eps = 0.0f;
+    bool defined() const { return sumsq != nullptr; }
+};
+
 struct StepContext {
     int T = 0, S = 0;
     const int32_t* token_ids = nullptr;      // [T]
@@ -182,6 +194,7 @@ struct StepContext {
     int64_t residual_width = 0;
     int* gemm_error = nullptr;               // device words where kernels with bounded waits report giving up
     int* attention_error = nullptr;
+    RowScale row_scale;                      // set by an arrangement around a consumer that takes unscaled rows, else undefined
     std::map<std::string, StepArray> arrays; // what parts added through StepPlan, by name
     const Json* options = nullptr;           // kernel choices for tests ("decode_kernel": "cp_async", ...)
 
@@ -260,6 +273,13 @@ public:
     // rows == nullptr: all T rows, and the pending addend is folded into the stream for good; else the n_rows
     // gathered rows (the stream keeps its pending addend).
     virtual Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows = nullptr, int n_rows = 0) = 0;
+    // As forward() over all rows, for a consumer that applies the row's factor itself: a norm that can leave the
+    // factor out returns the weighted, unscaled rows and describes the factor in *scale; one that cannot returns what
+    // forward() returns and leaves *scale undefined.
+    virtual Tensor forward_unscaled(ResidualStream& stream, StepContext& ctx, RowScale* scale) {
+        *scale = RowScale();
+        return forward(stream, ctx);
+    }
 };
 
 class QE_API PositionEncoding : public Part {
@@ -279,12 +299,16 @@ public:
     virtual CacheNeed cache_need() const { return CacheNeed(); }
     // x [T, E] in the compute dtype (already normed); rows of one request arrive in order.
     virtual Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) = 0;
+    // True: in this step the mixer applies ctx.row_scale to what its first product gives, so the norm in front may
+    // leave the row's factor out (see RowScale).  A mixer that says nothing always gets finished rows.
+    virtual bool takes_unscaled_rows(const StepContext&) const { return false; }
 };
 
 class QE_API FeedForward : public Part {
 public:
     using Part::Part;
     virtual Addend forward(const Tensor& x, StepContext& ctx) = 0;
+    virtual bool takes_unscaled_rows(const StepContext&) const { return false; }     // as Mixer's
 };
 
 class QE_API Embedding : public Part {

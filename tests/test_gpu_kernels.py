@@ -206,6 +206,74 @@ def test_gemm_tcgen05_adds_into_the_output(M, N, K):
         assert torch.equal(out, base + prod)
 
 
+@pytest.mark.parametrize("T,E,splits,yd", [(1, 512, 1, torch.bfloat16), (8, 4096, 9, torch.bfloat16), (5, 1000, 3, torch.bfloat16),
+                                           (33, 5120, 6, torch.bfloat16), (3, 96, 2, torch.float32)])
+def test_a_norm_that_leaves_the_row_factor_to_its_consumer(T, E, splits, yd):
+    """add_weight_sumsq: x += the addends, y = x * weight, and the row's sum of squares in chunks of 512 columns; the
+    consumer's factor rsqrt(sum / E + eps) times y is the RMSNorm.  Then the two consumers: the few-token product
+    (with and without the SwiGLU) whose epilogue applies the factor, and the per-head norm behind a qkv product."""
+    from purhie_b200.csrc import gemm100, ops
+    x = rnd(T, E, seed=31)
+    add = rnd(splits, T, E, seed=32, scale=0.3)
+    w = (torch.rand(E, generator=torch.Generator().manual_seed(33)) + 0.5).to(DEV)
+    v = x.double() + add.double().sum(0)
+    y = torch.full((T, E), float("nan"), dtype=yd, device=DEV)
+    sumsq = ops.add_weight_sumsq(x, add, w, y, add_splits=splits)
+    assert sumsq.shape == (T, -(-E // 512))
+    assert rel(x, v) < 1e-6                                             # the stream holds the sum
+    assert rel(y, v * w.double()) < (4e-3 if yd == torch.bfloat16 else 1e-6)
+    chunks = torch.stack([(v[:, c:c + 512] ** 2).sum(-1) for c in range(0, E, 512)], -1)
+    assert rel(sumsq, chunks) < 1e-5
+    if yd != torch.bfloat16 or E % 8:
+        return
+    eps = 1e-5
+    factor = torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)          # float64
+    N = 264
+    wt = rnd(N, E, dtype=torch.bfloat16, seed=34, scale=0.2)
+    block_n = 16 if T <= 16 else 64
+    full = y.double() @ wt.double().T * factor                           # what the product of the finished rows would give
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm100.gemm(y, wt, out, swapped=True, block_n=block_n, row_sumsq=sumsq, row_width=E, row_eps=eps)
+    gemm100.check_errors(DEV)
+    assert rel(out, full) < 6e-3
+    act = torch.full((T, N // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm100.gemm(y, wt, act, swapped=True, block_n=block_n, swiglu=True, row_sumsq=sumsq, row_width=E, row_eps=eps)
+    gemm100.check_errors(DEV)
+    g, u = full[:, 0::2], full[:, 1::2]
+    assert rel(act, g / (1 + torch.exp(-g)) * u) < 8e-3
+
+
+@pytest.mark.parametrize("HQ,HKV,D,splits", [(4, 2, 128, 3), (3, 1, 48, 2)])
+def test_qk_norm_rope_applies_the_row_factor_before_the_bias(HQ, HKV, D, splits):
+    """The per-head norm kernel with a row factor: its result equals that of the same kernel fed rows that were
+    multiplied by the factor beforehand (bias added after the factor; the v heads scaled too)."""
+    from purhie_b200.csrc import ops
+    T, ps = 9, 8
+    width = (HQ + 2 * HKV) * D
+    qkv = rnd(splits, T, width, seed=41)
+    sumsq = (torch.rand(T, 3, generator=torch.Generator().manual_seed(42)) * 40 + 1).to(DEV)
+    row_width, eps = 77, 1e-4
+    factor = torch.rsqrt(sumsq.double().sum(-1) / row_width + eps).float()
+    bias = rnd(width, seed=43, scale=0.1)
+    qn, kn = rnd(D, seed=44).abs() + 0.5, rnd(D, seed=45).abs() + 0.5
+    pos = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * inv[None]
+    table = torch.cat([ang.cos(), ang.sin()], -1).float().to(DEV)
+    slots = torch.arange(T, dtype=torch.int32, device=DEV)
+    res = []
+    for scaled_before in (False, True):
+        src = qkv * factor[None, :, None] if scaled_before else qkv
+        pool = torch.zeros(2, 1, 2, HKV, ps, D, device=DEV)
+        q = torch.empty(T, HQ, D, device=DEV)
+        ops.qk_norm_rope_kv_write(src.contiguous(), q, pos, num_heads=HQ, num_kv_heads=HKV, head_dim=D, eps=1e-6, q_norm=qn, k_norm=kn,
+                                  bias=bias, cos_sin=table, n_rot=D, slot_mapping=slots, k_base=pool[0, 0, 0], v_base=pool[0, 0, 1],
+                                  page_stride=pool.stride(0), page_size=ps, splits=splits,
+                                  row_sumsq=None if scaled_before else sumsq, row_width=row_width, row_eps=eps)
+        res.append((q, pool))
+    assert rel(res[0][0], res[1][0]) < 2e-6 and rel(res[0][1], res[1][1]) < 2e-6
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address():
     from purhie_b200.csrc import gemm100
     from purhie_b200.csrc.ops import KernelError
