@@ -298,8 +298,10 @@ private:
         const int n = ctx.n_decode_rows;
         const bool bulk_ok = cache.page_size % 8 == 0 && kBlockKeys % cache.page_size == 0 && cache.num_pages > 0;
         const bool bulk = bulk_ok && ctx.option("decode_kernel") != "cp_async";
-        const int splits = bulk ? bulk_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_)
-                                : decode_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_);
+        int splits = (int)ctx.option_int("decode_splits");            // a test's choice, else what the cost model picks
+        if (splits < 1 || splits > kMaxSplits)
+            splits = bulk ? bulk_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_)
+                          : decode_splits(n, kv_heads_, ctx.decode_max_ctx, sms, window_);
         float *part_o = nullptr, *part_ml = nullptr;
         if (splits > 1) {
             part_o = ws.get("attn_part_o", {n, heads_, splits, head_dim_}, DType::F32).as<float>();
