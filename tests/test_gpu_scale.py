@@ -186,6 +186,32 @@ def test_whole_models_in_float32_and_bfloat16(shape, needs_gb):
         assert not same_top1_or_near_tie(got, ref, 1e-1)
 
 
+def test_the_norm_factor_applied_by_the_consumer_gives_what_the_norm_kernel_gives():
+    """Few-token steps leave the norm's factor per row to the consumer of the normed rows (the gate/up product's
+    epilogue, the per-head norm behind the qkv product); the step option "row_factor": "norm" keeps it in the norm's
+    kernel.  Both in bfloat16 at the 8B-class layer shape, a short prompt, eight requests decoding side by side and a
+    chunk of 100 tokens: the two differ by bfloat16 roundings only, and both stay as close to float32."""
+    from purhie_b200.engine import Engine, StepEntry
+    reqs = [ids(40 + 11 * i, 400 + i) for i in range(8)]
+    got = {}
+    for name, dtype, opts in (("f32", "float32", None), ("consumer", "bfloat16", None), ("norm", "bfloat16", {"row_factor": "norm"})):
+        eng = Engine.from_random(SHAPES["8b"], 7, dtype=dtype, page_size=16, max_tokens=4096, max_requests=9, step_options=opts)
+        rows = []
+        for i, r in enumerate(reqs):
+            eng.add_request(i)
+            rows.append(eng.step([StepEntry(i, r[:-4], [len(r) - 5])]))
+        for k in range(4):
+            rows.append(eng.step([StepEntry(i, [r[len(r) - 4 + k]], [0]) for i, r in enumerate(reqs)]))
+        eng.add_request("chunk")
+        rows.append(eng.step([StepEntry("chunk", ids(100, 77), [0, 50, 99])]))
+        got[name] = np.concatenate(rows)
+        eng.close()
+    base = rel(got["norm"], got["f32"])
+    assert base < 3e-2
+    assert rel(got["consumer"], got["f32"]) < 1.5 * base + 2e-3
+    assert rel(got["consumer"], got["norm"]) < 2e-2 and not np.isnan(got["consumer"]).any()
+
+
 def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
     """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
     8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
