@@ -114,6 +114,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the mixed step")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="run one phase only, with few launches around it (for profiling under ncu)")
+    ap.add_argument("--step-options", default="", metavar="JSON",
+                    help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
     ap.add_argument("--leave-out", default="", metavar="NAMES",
                     help="with --phase decode: launchers (comma separated, e.g. add_rmsnorm,decode_bulk) that the timed steps "
                          "skip; the difference to a run without shows what they cost inside the graph (no benchmark value)")
@@ -141,7 +143,8 @@ def main():
     if args.phase != "all":
         args.no_points = True
     kv_tokens = max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64
-    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 2, page_size=16, kv_tokens=kv_tokens)
+    step_options = {"step": json.loads(args.step_options)} if args.step_options else {}
+    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 2, page_size=16, kv_tokens=kv_tokens, **step_options)
     eng = Engine.attach(model)
     rng = np.random.default_rng(SEED)
     ids = lambda n: rng.integers(0, cfg.vocab_size, size=n).tolist()

@@ -52,12 +52,20 @@ struct GemmParams {
     int swiglu;          // 1: columns are (gate, up) pairs; out[a, j] = silu(D[a, 2j]) * D[a, 2j + 1] (plain orientation)
     long long ld;        // row length of out
     long long split_stride;
-    // Swapped orientation with bfloat16 output: a factor per token that the norm in front left out of the activations,
-    // rsqrt(sum over the chunks of row_sumsq[token][chunk] / row_width + row_eps), applied to the accumulator before
-    // anything else happens to it (the product is linear in its rows).  Null: none.
+    // A factor per token that the norm in front left out of the activations, rsqrt(sum over the chunks of
+    // row_sumsq[token][chunk] / row_width + row_eps), applied to the accumulator before anything else happens to it
+    // (the product is linear in its rows).  Swapped orientation: bfloat16 output; plain orientation: tiles of 256
+    // columns, one split, no accumulate.  Null: none.
     const float* row_sumsq;
     int row_chunks, row_width;
     float row_eps;
+    // Plain orientation with accumulate, tiles of 256 columns: what the norm after this addition would do is done here.
+    // Beside out += product, the new rows times norm_weight go to norm_rows (bfloat16, [rows_a, ld]) and each row's sum
+    // of squares over this tile's columns to norm_sumsq[row][tile] ([rows_a, b_tiles]): the rows lack the factor
+    // rsqrt(sum over the tiles / ld + eps), which their consumer applies (row_sumsq above).  Null: none.
+    const float* norm_weight;
+    __nv_bfloat16* norm_rows;
+    float* norm_sumsq;
     int* error_flag;
 };
 
@@ -177,9 +185,18 @@ template <int BN> struct TileConfig {
     static constexpr int BUDGET = (CTAS_PER_SM == 2 ? 104 : 200) * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 10 ? 10 : (BUDGET / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : 2 * BN;          // a power of two: BN is one
-    static constexpr int STAGING_BYTES = 4 * 32 * 32 * 2;                   // per epilogue warp: 32 tokens x 32 features, bfloat16
+    // per epilogue warp: 32 tokens x 32 features in bfloat16 (swapped), 32 rows x 32 columns in float32 (plain, tiles of 256)
+    static constexpr int STAGING_BYTES = 4 * 32 * 32 * (BN == 256 ? 4 : 2);
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */ + STAGING_BYTES;
 };
+
+// Plain orientation: the factor that the norm in front left out of row a of the activations.
+__device__ __forceinline__ float plain_row_factor(const GemmParams& p, int a) {
+    if (a >= p.rows_a) return 1.0f;
+    float s = 0.0f;
+    for (int k = 0; k < p.row_chunks; ++k) s += p.row_sumsq[(size_t)a * p.row_chunks + k];
+    return rsqrtf(s / (float)p.row_width + p.row_eps);
+}
 
 // One chunk of CH accumulator columns of row a, starting at column b0 + c of the tile, to its place in out.
 template <int CH>
@@ -273,6 +290,86 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t*
             for (int j = 0; j < CH; ++j)
                 if (b0 + c + j < p.rows_b) o[(size_t)(b0 + c + j) * p.ld] = __uint_as_float(r[j]);
         }
+    }
+}
+
+// Plain orientation, tiles of 256 columns, out += product: 32 columns of the warp's 32 rows pass through the warp's
+// staging buffer (float32 [32][32], 16-byte slots swizzled by the row), so that lanes 8k .. 8k + 7 take row
+// 4 it + k, four columns each, and the values that are added to can be asked for a chunk ahead, row by row, while the
+// chunk before is still being worked on (a thread that walked along its own accumulator row would wait for its loads
+// once per chunk, with nothing else to do).
+// Vector form: every lane's four columns exist and are 16-byte aligned; else element by element, without the load ahead.
+__device__ __forceinline__ bool accumulate_in_vectors(const GemmParams& p) {
+    return (p.ld & 3) == 0 && ((uintptr_t)p.out & 15) == 0 && (p.rows_b & 3) == 0;
+}
+// The values of out that chunk c of the warp's rows is added to (zeros outside of out).
+__device__ __forceinline__ void load_accumulate_chunk(const GemmParams& p, int row0, int lane, int b0, int c, float4* old) {
+    const int col = b0 + c + (lane & 7) * 4;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int a = row0 + it * 4 + (lane >> 3);
+        old[it] = (a < p.rows_a && col < p.rows_b) ? *(const float4*)((const float*)p.out + (size_t)a * p.ld + (size_t)col)
+                                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+}
+// r: this lane's accumulator row; old: what load_accumulate_chunk fetched for this chunk (vector form only).
+// With the norm ahead, the new rows times the norm's weight go to norm_rows, and ss[it] gathers this lane's share of
+// the sum of squares of row 4 it + lane / 8.  Every lane of the warp calls this.
+__device__ __forceinline__ void store_chunk_accumulate_staged(const GemmParams& p, const uint32_t* r, const float4* old, bool vectors,
+                                                              float* buf, int row0, int lane, int b0, int c, float* ss) {
+    float4* mine = (float4*)(buf + lane * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        mine[j ^ (lane & 7)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                           __uint_as_float(r[4 * j + 3]));
+    __syncwarp();
+    const int sub = lane >> 3, slot = lane & 7;
+    const int col = b0 + c + slot * 4;                               // first of this lane's four columns
+    const bool ahead = p.norm_weight != nullptr;
+    float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (ahead && vectors && col < p.rows_b) g = __ldg((const float4*)(p.norm_weight + col));
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int rr = it * 4 + sub, a = row0 + rr;
+        float4 v = ((const float4*)(buf + rr * 32))[slot ^ (rr & 7)];
+        if (a >= p.rows_a || col >= p.rows_b) continue;
+        const size_t at = (size_t)a * p.ld + (size_t)col;
+        float* o = (float*)p.out + at;
+        if (vectors) {
+            v = make_float4(old[it].x + v.x, old[it].y + v.y, old[it].z + v.z, old[it].w + v.w);
+            *(float4*)o = v;
+            if (ahead) {
+                ss[it] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * g.x, v.y * g.y), hi = __floats2bfloat162_rn(v.z * g.z, v.w * g.w);
+                *(uint2*)(p.norm_rows + at) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);   // ld % 4 == 0: 8-byte aligned
+            }
+        } else {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (col + k < p.rows_b) {
+                    const float x = o[k] + e[k];
+                    o[k] = x;
+                    if (ahead) {
+                        ss[it] += x * x;
+                        p.norm_rows[at + k] = __float2bfloat16_rn(x * __ldg(p.norm_weight + col + k));
+                    }
+                }
+        }
+    }
+    __syncwarp();                                                    // the buffer is written again for the next chunk
+}
+
+// After the last chunk of a tile: the sums of squares of the warp's rows over the tile's columns, to norm_sumsq.
+__device__ __forceinline__ void store_tile_sumsq(const GemmParams& p, float* ss, int row0, int lane, int tile_b) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        float s = ss[it];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        const int a = row0 + it * 4 + (lane >> 3);
+        if ((lane & 7) == 0 && a < p.rows_a) p.norm_sumsq[(size_t)a * p.b_tiles + tile_b] = s;
     }
 }
 
@@ -479,7 +576,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int i = 0; i < FR; ++i) {
                 factor[i] = 1.0f;
                 const int t = b0 + i * 32 + lane;
-                if (p.row_sumsq && i * 32 + lane < BN && t < p.rows_b) {
+                if (p.swapped && p.row_sumsq && i * 32 + lane < BN && t < p.rows_b) {
                     float s = 0.0f;
                     for (int k = 0; k < p.row_chunks; ++k) s += p.row_sumsq[(size_t)t * p.row_chunks + k];
                     factor[i] = rsqrtf(s / (float)p.row_width + p.row_eps);
@@ -490,11 +587,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int a = a0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             const size_t split_off = (size_t)split * (size_t)p.split_stride;
+            // plain orientation, tiles of 256 columns: the factor of this thread's row, and its sum of squares for the norm ahead
+            constexpr bool ROW_OPS = BN == 256;
+            const bool scale_row = ROW_OPS && !p.swapped && p.row_sumsq != nullptr;
+            float row_f = 1.0f;
+            float ss[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            if constexpr (ROW_OPS) row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
+            // out += product (tiles of 256 columns): the values added to are fetched one chunk ahead
+            const bool staged_add = ROW_OPS && !p.swapped && p.accumulate;
+            const bool vectors = staged_add && accumulate_in_vectors(p);
+            float4 old[ROW_OPS ? 8 : 1], old_next[ROW_OPS ? 8 : 1];
+            if constexpr (ROW_OPS) { if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, 0, old_next); }
 #pragma unroll 1
             for (int c = 0; c < BN; c += CH) {
                 uint32_t r[CH];
                 if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
+                if constexpr (ROW_OPS) {
+                    if (vectors) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) old[i] = old_next[i];
+                        if (c + CH < BN) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + CH, old_next);
+                    }
+                }
                 tmem_ld_wait();
+                if constexpr (ROW_OPS) {
+                    if (scale_row) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_f);
+                    }
+                }
                 if (p.swapped && p.out_bf16) {
                     float f = factor[0];                  // the register that holds this chunk's tokens, picked without an index
 #pragma unroll
@@ -502,7 +623,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     store_chunk_swapped_bf16<CH>(p, r, staging + q * 32 * 32, a0 + q * 32, lane, b0, c, f);
                 }
                 else if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
+                else if (ROW_OPS && staged_add) {
+                    if constexpr (ROW_OPS) store_chunk_accumulate_staged(p, r, old, vectors, (float*)staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                }
                 else store_chunk<CH>(p, r, a, b0, c, split_off);
+            }
+            if constexpr (ROW_OPS) {
+                if (!p.swapped && p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, b0 / BN);
             }
             tc_fence_before();
             __syncwarp();
@@ -540,7 +667,8 @@ constexpr int PAIR_B_BYTES = PAIR_HALF * BK * 2;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_TMEM_COLS = 2 * PAIR_BN;
-constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_STAGING_BYTES = 4 * 32 * 32 * 4;        // per epilogue warp: 32 rows x 32 columns, float32
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_STAGING_BYTES;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -590,6 +718,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    float* staging = (float*)(smem + STAGES * PAIR_STAGE_BYTES + 256);       // [4 warps][32 x 32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -687,17 +816,35 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const int tile = w / p.splits;
             const int a0 = (tile % a_tiles) * 2 * BM + (int)rank * BM, b0 = (tile / a_tiles) * PAIR_BN;
             const size_t split_off = (size_t)(w % p.splits) * (size_t)p.split_stride;
+            // out += product: the values added to are fetched one chunk ahead, the first while the products still run
+            const bool vectors = p.accumulate && accumulate_in_vectors(p);
+            float4 old[8], old_next[8];
+            if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, 0, old_next);
             if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
             tc_fence_after();
             const int a = a0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PAIR_BN);
+            const bool scale_row = p.row_sumsq != nullptr;
+            const float row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
+            float ss[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
             for (int c = 0; c < PAIR_BN; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
+                if (vectors) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) old[i] = old_next[i];
+                    if (c + 32 < PAIR_BN) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + 32, old_next);
+                }
                 tmem_ld_wait();
-                store_chunk<32>(p, r, a, b0, c, split_off);
+                if (scale_row) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_f);
+                }
+                if (p.accumulate) store_chunk_accumulate_staged(p, r, old, vectors, staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                else store_chunk<32>(p, r, a, b0, c, split_off);
             }
+            if (p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, b0 / PAIR_BN);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
@@ -783,7 +930,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (work < grid) grid = work;
     // the staging buffer of the bfloat16 epilogue lies last: launches that do not use it leave it out
-    const size_t bytes = (size_t)Cfg::SMEM_BYTES - (p.swapped && p.out_bf16 ? 0 : Cfg::STAGING_BYTES);
+    const bool staged = (p.swapped && p.out_bf16) || (!p.swapped && BN == 256 && p.accumulate);
+    const size_t bytes = (size_t)Cfg::SMEM_BYTES - (staged ? 0 : Cfg::STAGING_BYTES);
     launch_overlapped(kernel, dim3(grid), dim3(NUM_THREADS), bytes, stream, ma, mb, p);
     return check_launch("gemm_tcgen05");
 }
@@ -821,11 +969,31 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
 
 PH_DEFINE_LAST_ERROR(ph_gemm100)
 
+namespace {
+// Plain orientation: why the row operations asked for cannot be done, or null.
+const char* row_ops_refused(const float* row_sumsq, int row_chunks, int row_width, const float* norm_weight, const void* norm_rows,
+                            const float* norm_sumsq, int splits, int accumulate, int N) {
+    if (row_sumsq && (splits > 1 || accumulate || row_chunks < 1 || row_width < 1))
+        return "a factor per token goes with one split and without accumulate";
+    const int given = (norm_weight != nullptr) + (norm_rows != nullptr) + (norm_sumsq != nullptr);
+    if (given == 0) return nullptr;
+    if (given != 3) return "norm_weight, norm_rows and norm_sumsq come together";
+    if (!accumulate) return "the rows for the norm ahead are written together with the addition into the output";
+    if ((N & 3) || (((uintptr_t)norm_weight | (uintptr_t)norm_rows) & 15)) return "the norm ahead needs rows of a multiple of 4 elements and 16-byte aligned arrays";
+    return nullptr;
+}
+}  // namespace
+
 // The same product on pairs of CTAs (tcgen05 cta_group::2): tiles of 256 tokens x 256 features, plain orientation;
 // float32 partial results [splits][M, N] with splits > 1.  max_clusters: 0 or a cap on the number of CTA pairs.
 // accumulate: out (float32, one split, no activation) += the product.
+// row_sumsq .. row_eps: the factor per token that the activations lack (one split, no accumulate); norm_weight [N],
+// norm_rows (bfloat16 [M, N]), norm_sumsq (float32 [M, ceil(N / 256)]): with accumulate, what the norm after this
+// addition needs (GemmParams).  All may be null.
 PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                        int splits, int max_clusters, int swiglu, int accumulate, int* error_flag,
+                                        int splits, int max_clusters, int swiglu, int accumulate,
+                                        const float* row_sumsq, int row_chunks, int row_width, float row_eps,
+                                        const float* norm_weight, void* norm_rows, float* norm_sumsq, int* error_flag,
                                         cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05_pair: bad arguments (M %d, N %d, K %d)", M, N, K);
@@ -837,15 +1005,18 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     if (swiglu && ((N & 1) || splits > 1)) return fail(PH_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue needs an even N and one split");
     if (accumulate && (swiglu || splits > 1 || out_dtype != PH_F32))
         return fail(PH_ERR_ARG, "gemm_tcgen05_pair: adding into the output needs float32, one split and no activation");
+    if (const char* why = row_ops_refused(row_sumsq, row_chunks, row_width, norm_weight, norm_rows, norm_sumsq, splits, accumulate, N))
+        return fail(PH_ERR_ARG, "gemm_tcgen05_pair: %s", why);
     CUtensorMap ma, mb;
     if (!make_map(&ma, x, M, K, BM) || !make_map(&mb, w, N, K, PAIR_HALF))
         return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cuTensorMapEncodeTiled failed (rows %d / %d, K %d)", M, N, K);
     GemmParams p;
     p.rows_a = M; p.rows_b = N; p.K = K;
-    p.a_tiles = 0; p.b_tiles = 0; p.splits = splits; p.kblocks = kblocks;
+    p.a_tiles = 0; p.b_tiles = (N + PAIR_BN - 1) / PAIR_BN; p.splits = splits; p.kblocks = kblocks;
     p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
-    p.row_sumsq = nullptr; p.row_chunks = 0; p.row_width = 0; p.row_eps = 0.0f;
+    p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
+    p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
     return launch_pair(ma, mb, p, max_clusters, stream);
 }
 
@@ -855,10 +1026,12 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
 // (the formula of src/gpu_ops.hip:103-114 in the reference).
 // accumulate: out (float32, plain orientation, one split, no activation) += the product.
 // row_sumsq [M][row_chunks] (or null), row_width, row_eps: the activations lack a factor per token, see GemmParams;
-// taken by the swapped orientation with bfloat16 output only.
+// taken by the swapped orientation with bfloat16 output, and by the plain orientation with tiles of 256 columns.
+// norm_weight, norm_rows, norm_sumsq: as in the pair kernel (plain orientation, block_n 256, accumulate).
 PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
                                    int swapped, int block_n, int splits, int max_ctas, int swiglu, int accumulate,
                                    const float* row_sumsq, int row_chunks, int row_width, float row_eps,
+                                   const float* norm_weight, void* norm_rows, float* norm_sumsq,
                                    int* error_flag, cudaStream_t stream) {
     if (!x || !w || !out || !error_flag || M < 1 || N < 1 || K < 1 || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "gemm_tcgen05: bad arguments (M %d, N %d, K %d)", M, N, K);
@@ -870,8 +1043,16 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     if (swiglu && (splits > 1 || (N & 1) || (!swapped && block_n < 32)))
         return fail(PH_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue needs one split, an even N and, in the plain orientation, "
                                 "tiles of 32 features or more");
-    if (row_sumsq && (!swapped || out_dtype != PH_BF16 || splits > 1 || row_chunks < 1 || row_width < 1))
-        return fail(PH_ERR_ARG, "gemm_tcgen05: a factor per token goes with the swapped orientation, bfloat16 output and one split");
+    if (row_sumsq && swapped && (out_dtype != PH_BF16 || splits > 1 || row_chunks < 1 || row_width < 1))
+        return fail(PH_ERR_ARG, "gemm_tcgen05: in the swapped orientation a factor per token goes with bfloat16 output and one split");
+    if (!swapped) {
+        if ((row_sumsq || norm_weight || norm_rows || norm_sumsq) && block_n != 256)
+            return fail(PH_ERR_ARG, "gemm_tcgen05: in the plain orientation the row operations go with tiles of 256 columns");
+        if (const char* why = row_ops_refused(row_sumsq, row_chunks, row_width, norm_weight, norm_rows, norm_sumsq, splits, accumulate, N))
+            return fail(PH_ERR_ARG, "gemm_tcgen05: %s", why);
+    } else if (norm_weight || norm_rows || norm_sumsq) {
+        return fail(PH_ERR_ARG, "gemm_tcgen05: the rows for the norm ahead are written in the plain orientation only");
+    }
     if (accumulate && (swapped || swiglu || splits > 1 || out_dtype != PH_F32))
         return fail(PH_ERR_ARG, "gemm_tcgen05: adding into the output needs the plain orientation, float32, one split and no activation");
     const void* a = swapped ? w : x;
@@ -887,6 +1068,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
+    p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
     switch (block_n) {
         case 16: return launch<16>(ma, mb, p, max_ctas, stream);
         case 32: return launch<32>(ma, mb, p, max_ctas, stream);

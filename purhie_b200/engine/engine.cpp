@@ -65,6 +65,7 @@ Engine::~Engine() {
         if (s.p.event) cudaEventDestroy(s.p.event);
     for (int i = 0; i < 2; i++)
         if (meta_event_[i]) cudaEventDestroy(meta_event_[i]);
+    LaunchProfile::get().forget_stream(stream_);
     if (stream_) cudaStreamDestroy(stream_);
 }
 

@@ -251,10 +251,10 @@ void LaunchProfile::end() {
     if (!records_.empty()) cudaEventRecord(records_.back().stop, stream_);
 }
 void LaunchProfile::fold() {
-    cudaStreamSynchronize(stream_);
+    // waits on the events, not on the stream: the engine whose stream they were recorded on may be gone by now
     for (Record& r : records_) {
         float ms = 0;
-        if (cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess) {
+        if (cudaEventSynchronize(r.stop) == cudaSuccess && cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess) {
             Sum& s = sums_[r.name];
             s.calls++; s.ms += ms; s.bytes += r.bytes; s.flops += r.flops;
         }

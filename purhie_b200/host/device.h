@@ -122,8 +122,9 @@ struct FlashKernels {
 };
 struct GemmKernels {
     int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, const float*, int, int, float,
-                int*, cudaStream_t);
-    int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int*, cudaStream_t);
+                const float*, void*, float*, int*, cudaStream_t);
+    int (*gemm_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, const float*, int, int, float,
+                     const float*, void*, float*, int*, cudaStream_t);
     const char* (*last_error)(void);
 };
 
@@ -149,6 +150,7 @@ public:
     bool on() const { return enabled_; }
     void set_enabled(bool on) { enabled_ = on; }
     void set_stream(cudaStream_t s) { stream_ = s; }
+    void forget_stream(cudaStream_t s) { if (stream_ == s) stream_ = nullptr; }      // before s is destroyed
     void note_cost(double bytes, double flops) { pending_bytes_ = bytes; pending_flops_ = flops; }   // of the next launch
     void begin(const char* call_text);
     void end();

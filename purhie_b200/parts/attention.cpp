@@ -228,9 +228,14 @@ public:
 
     // Few rows in bfloat16: the qkv product's float32 sums are linear in the rows, and the kernel that adds them up
     // (per-head norm, rotation, cache write) multiplies by the factor the norm in front left out.
+    // Many rows: either the qkv product's epilogue applies the factor (K whole), or K is cut and the same kernel as
+    // above adds up the parts.
     bool takes_unscaled_rows(const StepContext& ctx) const override {
-        return compute_dtype == DType::BF16 && qkv_proj_.swapped_for(ctx.T, true, false) &&
-               (!q_only_proj_.defined() || q_only_proj_.swapped_for(ctx.T, true, false));
+        auto takes = [&](const Linear& proj) {
+            return proj.swapped_for(ctx.T, true, false) || proj.applies_row_scale(ctx.T, compute_dtype, false, true) ||
+                   proj.gives_partial_sums(ctx.T, true);
+        };
+        return compute_dtype == DType::BF16 && takes(qkv_proj_) && (!q_only_proj_.defined() || takes(q_only_proj_));
     }
 
     // ---- step ----------------------------------------------------------------------------------------------------
@@ -241,7 +246,10 @@ public:
         const GroupStep& g = ctx.groups.at(cache.group);
         const CoreKernels& core = core_kernels();
         const Linear& proj = cache.writable ? qkv_proj_ : q_only_proj_;
-        Addend qkv = proj(x, ctx, "qkv", dt, T, true);
+        // rows without their factor (RowScale): the product's epilogue applies it where it can, else the kernel behind it
+        const bool scale_in_product = ctx.row_scale.defined() && proj.applies_row_scale(T, dt, false, true);
+        Addend qkv = proj(x, ctx, "qkv", dt, T, true, false, nullptr, scale_in_product ? &ctx.row_scale : nullptr);
+        const RowScale later = scale_in_product ? RowScale() : ctx.row_scale;
         const int kv_heads_written = cache.writable ? kv_heads_ : 0;
         Tensor q = ws.get("q", {T, heads_, head_dim_}, dt);
         const int column = position_ ? position_->position_column() : 0;
@@ -253,8 +261,7 @@ public:
             position_ ? position_->n_rot() : 0, table_.defined() ? (int)table_.shape[0] : 0, positions,
             cache.writable ? g.slot_mapping : nullptr, q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype,
             cache.page_stride, cache.page_size, T, heads_, kv_heads_written, head_dim_,
-            position_ && position_->interleaved() ? 1 : 0, ctx.row_scale.sumsq, ctx.row_scale.chunks, ctx.row_scale.width,
-            ctx.row_scale.eps, ctx.stream));
+            position_ && position_->interleaved() ? 1 : 0, later.sumsq, later.chunks, later.width, later.eps, ctx.stream));
         Tensor out = ws.get("attn_out", {T, q_width_}, dt);
         const int32_t* abs_positions = ctx.position_column(0);       // the mask always follows the index in the request
         if (use_flash()) {
@@ -265,7 +272,7 @@ public:
                                                    cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
                                                    out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, ctx.stream));
         }
-        return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual);
+        return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 
 private:

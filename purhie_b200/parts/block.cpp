@@ -23,15 +23,27 @@ public:
         // a consumer that applies the row's factor itself lets the norm in front leave it out (RowScale)
         // (the option "row_factor": "norm" keeps the factor in the norm, for comparing the two forms)
         const bool may_defer = ctx.option("row_factor") != "norm";
+        // and a part whose last product adds into the residual itself may do the pass of the norm behind it there
+        // (NormAhead; the option "norm_ahead": "off" keeps every norm a kernel of its own)
+        const bool may_work_ahead = may_defer && ctx.option("norm_ahead") != "off";
+        const bool ff_unscaled = may_defer && ff_->takes_unscaled_rows(ctx);
         ctx.row_scale = RowScale();
         Tensor xn = may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->forward_unscaled(stream, ctx, &ctx.row_scale)
                                                                   : mixer_norm_->forward(stream, ctx);
+        ctx.norm_ahead = may_work_ahead && ff_unscaled ? ff_norm_->offer(ctx) : NormAhead();
         stream.add(mixer_->forward(xn, ctx, cache));
+        stream.prepare(ctx.norm_ahead);
         ctx.row_scale = RowScale();
-        xn = may_defer && ff_->takes_unscaled_rows(ctx) ? ff_norm_->forward_unscaled(stream, ctx, &ctx.row_scale)
-                                                        : ff_norm_->forward(stream, ctx);
+        xn = ff_unscaled ? ff_norm_->forward_unscaled(stream, ctx, &ctx.row_scale) : ff_norm_->forward(stream, ctx);
+        ctx.norm_ahead = may_work_ahead ? ctx.next_layer_norm : NormAhead();
         stream.add(ff_->forward(xn, ctx));
+        stream.prepare(ctx.norm_ahead);
         ctx.row_scale = RowScale();
+        ctx.norm_ahead = NormAhead();
+    }
+    NormAhead first_norm(const StepContext& ctx) const override {
+        const bool may_defer = ctx.option("row_factor") != "norm";
+        return may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->offer(ctx) : NormAhead();
     }
 private:
     std::shared_ptr<Norm> mixer_norm_, ff_norm_;

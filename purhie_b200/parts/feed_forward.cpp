@@ -41,7 +41,7 @@ public:
         return (gate_up_.fast() || down_.fast()) ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
     }
 
-    // few rows in bfloat16: the gate/up product's epilogue applies the norm's factor per row before the activation
+    // bfloat16: the gate/up product's epilogue applies the norm's factor per row before the activation
     bool takes_unscaled_rows(const StepContext& ctx) const override {
         return compute_dtype == DType::BF16 && gate_up_.applies_row_scale(ctx.T, compute_dtype, true);
     }
@@ -57,7 +57,7 @@ public:
             QE_LAUNCH(k, k.swiglu(gu.tensor.data, gu.tensor.code(), gu.splits, (long long)T * 2 * inter_, act.data, act.code(), T,
                                   (int)inter_, ctx.stream));
         }
-        return down_(act, ctx, "ff_out", DType::F32, T, true, false, ctx.residual);
+        return down_(act, ctx, "ff_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 
 private:

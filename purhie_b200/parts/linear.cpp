@@ -88,13 +88,23 @@ bool Linear::swapped_for(int rows, bool allow_split, bool fused_epilogue) const 
     return p.swapped && !p.pair;
 }
 
-bool Linear::applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu) const {
-    // the fused activation keeps K whole and writes bfloat16 from the swapped epilogue, which is where the factor goes
-    return out_dtype == DType::BF16 && fuse_swiglu && weight_.shape[0] % 2 == 0 && swapped_for(rows, true, true);
+bool Linear::applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu, bool allow_split) const {
+    if (!fast_) return false;
+    const bool fused = fuse_swiglu && weight_.shape[0] % 2 == 0;
+    const GemmPlan p = plan_gemm(rows, (int)weight_.shape[0], (int)weight_.shape[1], sm_count(), allow_split, fused);
+    // few rows: the fused activation keeps K whole and writes bfloat16 from the swapped epilogue, which is where the factor goes
+    if (p.swapped) return out_dtype == DType::BF16 && fused;
+    // many rows: the epilogue of the 256-feature tiles, whenever it holds whole sums
+    return p.block_n == 256 && p.splits == 1;
+}
+
+bool Linear::gives_partial_sums(int rows, bool allow_split) const {
+    if (!fast_) return false;
+    return plan_gemm(rows, (int)weight_.shape[0], (int)weight_.shape[1], sm_count(), allow_split, false).splits > 1;
 }
 
 Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
-                          bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale) const {
+                          bool allow_split, bool fuse_swiglu, float* add_into, const RowScale* scale, NormAhead* ahead) const {
     const int M = rows, N = (int)weight_.shape[0], K = (int)weight_.shape[1];
     Workspace& ws = *ctx.workspace;
     const CoreKernels& core = core_kernels();
@@ -105,7 +115,7 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
         x = x32;
     }
     const bool scaled = scale && scale->defined();
-    if (scaled && !(fast_ && x.dtype == DType::BF16 && applies_row_scale(M, out_dtype, fuse_swiglu)))
+    if (scaled && !(fast_ && x.dtype == DType::BF16 && !add_into && applies_row_scale(M, out_dtype, fuse_swiglu, allow_split)))
         throw KernelError(label_ + ": rows without their factor reached a product that cannot apply it");
     if (!(fast_ && x.dtype == DType::BF16)) {
         Tensor out = ws.get(out_name, {M, N}, out_dtype);
@@ -117,16 +127,31 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
     const GemmKernels& g = gemm_kernels();
     const bool fused = fuse_swiglu && N % 2 == 0;
     GemmPlan p = plan_gemm(M, N, K, sm_count(), allow_split, fused);
-    auto run = [&](Tensor& out, int splits, bool swiglu, bool accumulate) {
+    auto run = [&](Tensor& out, int splits, bool swiglu, bool accumulate, NormAhead* work_ahead = nullptr) {
         if (LaunchProfile::get().on())      // what the product has to move and to compute: the weight once, x, and its result
             LaunchProfile::get().note_cost(2.0 * N * K + 2.0 * M * K + (double)out.bytes(), 2.0 * M * N * K);
+        const float* sumsq = scaled ? scale->sumsq : nullptr;
+        const int chunks = scaled ? scale->chunks : 0, width = scaled ? scale->width : 0;
+        const float eps = scaled ? scale->eps : 0.0f;
+        const float* ahead_weight = nullptr;
+        void* ahead_rows = nullptr;
+        float* ahead_sumsq = nullptr;
+        if (work_ahead) {
+            // the norm behind this addition: its weighted rows and their sums of squares per tile of 256 features
+            const int tiles = ceil_div(N, 256);
+            work_ahead->rows = ws.get("norm_ahead_rows", {M, N}, DType::BF16);
+            Tensor sums = ws.get("norm_ahead_sumsq", {M, tiles}, DType::F32);
+            work_ahead->scale.sumsq = sums.as<float>(); work_ahead->scale.chunks = tiles;
+            work_ahead->scale.width = N; work_ahead->scale.eps = work_ahead->eps;
+            ahead_weight = work_ahead->weight; ahead_rows = work_ahead->rows.data; ahead_sumsq = sums.as<float>();
+        }
         if (p.pair)
-            QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, splits, 0, swiglu, accumulate,
-                                     ctx.gemm_error, ctx.stream));
+            QE_LAUNCH(g, g.gemm_pair(x.data, weight_.data, out.data, out.code(), M, N, K, splits, 0, swiglu, accumulate, sumsq, chunks,
+                                     width, eps, ahead_weight, ahead_rows, ahead_sumsq, ctx.gemm_error, ctx.stream));
         else
             QE_LAUNCH(g, g.gemm(x.data, weight_.data, out.data, out.code(), M, N, K, p.swapped, p.block_n, splits, 0, swiglu,
-                                accumulate, scaled ? scale->sumsq : nullptr, scaled ? scale->chunks : 0, scaled ? scale->width : 0,
-                                scaled ? scale->eps : 0.0f, ctx.gemm_error, ctx.stream));
+                                accumulate, sumsq, chunks, width, eps, ahead_weight, ahead_rows, ahead_sumsq, ctx.gemm_error,
+                                ctx.stream));
     };
     if (fused && (p.swapped || p.splits == 1)) {
         // K stays whole, so that the epilogue holds whole sums and can apply the activation; with few tokens the
@@ -138,7 +163,8 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
     if (add_into && !p.swapped && p.splits == 1 && ctx.residual_width == N) {
         // many tokens, K whole: the residual sum happens in the epilogue and the product never goes to memory
         Tensor target(add_into, DType::F32, {M, N});
-        run(target, 1, false, true);
+        const bool work_ahead = ahead && ahead->offered() && ahead->width == N && p.block_n == 256 && N % 4 == 0;
+        run(target, 1, false, true, work_ahead ? ahead : nullptr);
         return Addend();
     }
     Tensor out = p.splits > 1 ? ws.get(out_name + "_partial", {p.splits, M, N}, DType::F32) : ws.get(out_name, {M, N}, out_dtype);

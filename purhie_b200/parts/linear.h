@@ -37,14 +37,19 @@ public:
     // in its epilogue and the result [rows, out / 2] comes back marked activated.  add_into (float32 [rows, out]):
     // where the kernel can add the product there in its epilogue it does, and the addend comes back empty.
     // scale: the rows of x lack a factor per row (RowScale); only where applies_row_scale() is true, and then the
-    // kernel's epilogue multiplies by it.
+    // kernel's epilogue multiplies by it.  ahead (with add_into, for a part's last product): the norm that follows
+    // the addition; where the kernel adds in its epilogue and can, it fills ahead->rows and ahead->scale (NormAhead).
     Addend operator()(const Tensor& x, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
                       bool allow_split = false, bool fuse_swiglu = false, float* add_into = nullptr,
-                      const RowScale* scale = nullptr) const;
+                      const RowScale* scale = nullptr, NormAhead* ahead = nullptr) const;
     // Few rows on the tensor-core kernel: the weight fills the wide side of the instruction (what plan_gemm calls
     // swapped).  Its partial sums are linear in the rows, and its bfloat16 epilogue can apply a factor per row.
     bool swapped_for(int rows, bool allow_split, bool fused_epilogue) const;
-    bool applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu) const;
+    // The product's own epilogue multiplies by the rows' factor: few rows with the fused activation; many rows
+    // (tiles of 256 features) whenever K stays whole and nothing is added into the output.
+    bool applies_row_scale(int rows, DType out_dtype, bool fuse_swiglu, bool allow_split = true) const;
+    // Many rows, K cut into parts: float32 partial sums, linear in the rows, so whoever adds them up can apply the factor.
+    bool gives_partial_sums(int rows, bool allow_split) const;
 private:
     Tensor weight_;
     std::string label_;

@@ -92,9 +92,12 @@ Tensor DecoderModel::forward(StepContext& ctx, const std::vector<CacheView>& vie
     ResidualStream stream;
     stream.x = embedding_->forward(ctx);
     for (size_t i = 0; i < spec_.schedule.size(); i++) {
+        // a layer learns which norm the next entry of the run order starts with: its last product may work ahead for it
+        ctx.next_layer_norm = i + 1 < spec_.schedule.size() ? layers_[spec_.schedule[i + 1].layer]->first_norm(ctx) : NormAhead();
         layers_[spec_.schedule[i].layer]->forward(stream, ctx, views[i]);
         if (after_entry) after_entry((int)i, stream, ctx);
     }
+    ctx.next_layer_norm = NormAhead();
     if (n_want == 0) return Tensor();
     Tensor xn = final_norm_->forward(stream, ctx, want_rows, n_want);
     return head_->forward(xn, ctx, n_want);

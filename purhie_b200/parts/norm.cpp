@@ -31,6 +31,13 @@ public:
     // into the factor (bfloat16 model, rows of a multiple of four elements; else the ordinary form).
     Tensor forward_unscaled(ResidualStream& stream, StepContext& ctx, RowScale* scale) override {
         *scale = RowScale();
+        if (stream.prepared.done() && stream.prepared.norm == this && !stream.has_pending) {
+            // the product that added into the stream did this norm's pass in its epilogue
+            Tensor rows = stream.prepared.rows;
+            *scale = stream.prepared.scale;
+            stream.clear();
+            return rows;
+        }
         if (compute_dtype != DType::BF16 || size_ % 4) return forward(stream, ctx, nullptr, 0);
         constexpr int kChunk = 512;                                   // columns per CTA of the kernel
         const int chunks = (int)((size_ + kChunk - 1) / kChunk);
@@ -44,6 +51,13 @@ public:
         stream.clear();
         scale->sumsq = sumsq.as<float>(); scale->chunks = chunks; scale->width = (int)size_; scale->eps = (float)eps_;
         return out;
+    }
+
+    NormAhead offer(const StepContext&) const override {
+        NormAhead a;
+        if (compute_dtype != DType::BF16 || size_ % 4) return a;
+        a.weight = weight_.as<float>(); a.norm = this; a.width = (int)size_; a.eps = (float)eps_;
+        return a;
     }
 
 private:

@@ -171,6 +171,21 @@ struct RowScale {
     bool defined() const { return sumsq != nullptr; }
 };
 
+// The norm that follows a part's addition into the residual, offered to the part's last product.  A product that adds
+// into the residual in its own epilogue may do that norm's pass over the rows there as well: the weighted, unscaled
+// rows in bfloat16 and their sums of squares (RowScale).  The norm then finds them in the stream and launches nothing.
+// Offering costs nothing and binds nobody: a product that cannot do it leaves `rows` undefined.
+struct NormAhead {
+    const float* weight = nullptr;           // offered: [width] float32 on the device (null: nothing offered)
+    const void* norm = nullptr;              // the Norm that made the offer and may pick the rows up
+    int width = 0;
+    float eps = 0.0f;
+    Tensor rows;                             // done: [T, width] bfloat16, (x + addend) * weight
+    RowScale scale;                          // done: the factor the rows lack
+    bool offered() const { return weight != nullptr; }
+    bool done() const { return rows.defined(); }
+};
+
 struct StepContext {
     int T = 0, S = 0;
     const int32_t* token_ids = nullptr;      // [T]
@@ -195,6 +210,8 @@ struct StepContext {
     int* gemm_error = nullptr;               // device words where kernels with bounded waits report giving up
     int* attention_error = nullptr;
     RowScale row_scale;                      // set by an arrangement around a consumer that takes unscaled rows, else undefined
+    NormAhead norm_ahead;                    // set by an arrangement around a part: the norm after the part's addition
+    NormAhead next_layer_norm;               // set by the model around a layer: the first norm of the layer that runs next
     std::map<std::string, StepArray> arrays; // what parts added through StepPlan, by name
     const Json* options = nullptr;           // kernel choices for tests ("decode_kernel": "cp_async", ...)
 
@@ -226,11 +243,15 @@ struct ResidualStream {
     Tensor x;
     Addend pending;
     bool has_pending = false;
+    NormAhead prepared;                      // rows that the last product left for the norm that comes next (x is complete)
     void add(Addend a) {
         if (has_pending) throw Error(kInvalidState, "the residual stream already has a pending addend");
+        prepared = NormAhead();
         if (a.tensor.defined()) { pending = std::move(a); has_pending = true; }   // undefined: the part added into x itself
     }
-    void clear() { has_pending = false; pending = Addend(); }
+    // after add(): what the part's last product did for the norm ahead (nothing, if it did nothing)
+    void prepare(const NormAhead& ahead) { prepared = (!has_pending && ahead.done()) ? ahead : NormAhead(); }
+    void clear() { has_pending = false; pending = Addend(); prepared = NormAhead(); }
 };
 
 // ---- building ---------------------------------------------------------------------------------------------------
@@ -280,6 +301,9 @@ public:
         *scale = RowScale();
         return forward(stream, ctx);
     }
+    // What a product in front may do of this norm's work (NormAhead), if forward_unscaled() would pick it up from
+    // stream.prepared; a norm that has no such form offers nothing.
+    virtual NormAhead offer(const StepContext&) const { return NormAhead(); }
 };
 
 class QE_API PositionEncoding : public Part {
@@ -329,6 +353,9 @@ public:
     virtual std::vector<Part*> parts() = 0;
     virtual CacheNeed cache_need() const = 0;            // of the layer's mixer
     virtual void forward(ResidualStream& stream, StepContext& ctx, const CacheView& cache) = 0;
+    // The offer of the layer's first norm, if in this step it would take rows prepared by the layer in front (the
+    // model hands it to that layer as ctx.next_layer_norm).
+    virtual NormAhead first_norm(const StepContext&) const { return NormAhead(); }
 };
 
 // ---- registries -------------------------------------------------------------------------------------------------------

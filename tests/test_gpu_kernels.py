@@ -187,7 +187,7 @@ def test_gemm_tcgen05_swiglu_epilogue_with_few_tokens(M, N, K, block_n, out_dtyp
     assert rel(out, g / (1 + torch.exp(-g)) * u) < (3e-5 if out_dtype == torch.float32 else 6e-3)
 
 
-@pytest.mark.parametrize("M,N,K", [(300, 520, 200), (2048, 1024, 512)])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 200), (2048, 1024, 512), (300, 522, 200), (131, 257, 64)])
 def test_gemm_tcgen05_adds_into_the_output(M, N, K):
     """The residual sum in the epilogue: out += x w^T, on one CTA per tile and on pairs, with the bits of a product
     written out and added afterwards."""
@@ -204,6 +204,69 @@ def test_gemm_tcgen05_adds_into_the_output(M, N, K):
             gemm100.gemm(x, w, out, swapped=False, block_n=256, accumulate=True)
         gemm100.check_errors(DEV)
         assert torch.equal(out, base + prod)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 1000, 192), (128, 256, 64), (515, 516, 104), (1024, 4096, 1024)])
+def test_gemm_tcgen05_with_many_rows_does_the_work_of_the_norms_around_it(M, N, K):
+    """Plain orientation, tiles of 256 columns, on one CTA per tile and on pairs.  (1) Adding into the output, the
+    epilogue also leaves the new rows times the weight of the norm behind it, in bfloat16, and each row's sum of squares
+    per tile; the accumulated output keeps the bits it has without that.  (2) A factor per row that the norm in front
+    left out is applied before the store, the bfloat16 rounding and the activation."""
+    from purhie_b200.csrc import gemm100
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=51, scale=0.5), rnd(N, K, dtype=torch.bfloat16, seed=52, scale=0.1)
+    base = rnd(M, N, seed=53)
+    wn = (torch.rand(N, generator=torch.Generator().manual_seed(54)) + 0.5).to(DEV)
+    tiles = -(-N // 256)
+    sq = (torch.rand(M, 3, generator=torch.Generator().manual_seed(55)) * 100 + 1).to(DEV)
+    width, eps = 77, 1e-3
+    factor = torch.rsqrt(sq.double().sum(-1, keepdim=True) / width + eps)
+    prod = x.double() @ w.double().T
+    for pair in (False, True):
+        run = (lambda out, **kw: gemm100.gemm_pair(x, w, out, **kw)) if pair else \
+              (lambda out, **kw: gemm100.gemm(x, w, out, swapped=False, block_n=256, **kw))
+        plain = base.clone()
+        run(plain, accumulate=True)
+        out = base.clone()
+        rows = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        sumsq = torch.full((M, tiles), float("nan"), device=DEV)
+        run(out, accumulate=True, norm_ahead=(wn, rows, sumsq))
+        gemm100.check_errors(DEV)
+        assert torch.equal(out, plain)
+        assert torch.equal(rows, (out * wn).to(torch.bfloat16))
+        padded = torch.zeros(M, tiles * 256, dtype=torch.float64, device=DEV)
+        padded[:, :N] = out.double() ** 2
+        assert rel(sumsq, padded.view(M, tiles, 256).sum(-1)) < 1e-6
+        want = prod * factor
+        o32 = torch.full((M, N), float("nan"), device=DEV)
+        run(o32, row_sumsq=sq, row_width=width, row_eps=eps)
+        assert rel(o32, want) < 1e-5
+        ob = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        run(ob, row_sumsq=sq, row_width=width, row_eps=eps)
+        assert rel(ob, want) < 4e-3
+        act = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        run(act, swiglu=True, row_sumsq=sq, row_width=width, row_eps=eps)
+        gemm100.check_errors(DEV)
+        g, u = want[:, 0::2], want[:, 1::2]
+        assert rel(act, g / (1 + torch.exp(-g)) * u) < 6e-3
+
+
+def test_gemm_tcgen05_refuses_row_work_it_cannot_do():
+    from purhie_b200.csrc import gemm100
+    from purhie_b200.csrc.ops import KernelError
+    x, w = rnd(128, 64, dtype=torch.bfloat16), rnd(256, 64, dtype=torch.bfloat16)
+    out = torch.zeros(128, 256, device=DEV)
+    ahead = (torch.ones(256, device=DEV), torch.empty(128, 256, dtype=torch.bfloat16, device=DEV), torch.empty(128, 1, device=DEV))
+    sq = torch.ones(128, 2, device=DEV)
+    with pytest.raises(KernelError, match="together with the addition"):
+        gemm100.gemm_pair(x, w, out, norm_ahead=ahead)                                    # not adding into the output
+    with pytest.raises(KernelError, match="tiles of 256"):
+        gemm100.gemm(x, w, out, swapped=False, block_n=128, accumulate=True, norm_ahead=ahead)
+    with pytest.raises(KernelError, match="plain orientation only"):
+        gemm100.gemm(x, w, out, swapped=True, block_n=128, norm_ahead=ahead)
+    with pytest.raises(KernelError, match="without accumulate"):
+        gemm100.gemm_pair(x, w, out, accumulate=True, row_sumsq=sq, row_width=64, row_eps=1e-6)
+    with pytest.raises(KernelError, match="norm_ahead wants"):
+        gemm100.gemm_pair(x, w, out, accumulate=True, norm_ahead=(ahead[0], ahead[1], torch.empty(128, 3, device=DEV)))
 
 
 @pytest.mark.parametrize("T,E,splits,yd", [(1, 512, 1, torch.bfloat16), (8, 4096, 9, torch.bfloat16), (5, 1000, 3, torch.bfloat16),

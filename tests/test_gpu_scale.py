@@ -212,6 +212,49 @@ def test_the_norm_factor_applied_by_the_consumer_gives_what_the_norm_kernel_give
     assert rel(got["consumer"], got["norm"]) < 2e-2 and not np.isnan(got["consumer"]).any()
 
 
+def test_the_norm_done_in_the_epilogue_of_the_product_in_front_gives_what_its_own_kernel_gives():
+    """With many rows the o and down products add into the residual in their epilogue and do the pass of the norm
+    behind them there as well (weighted rows and sums of squares per tile; the consumer applies the factor).  Step
+    options switch that off ("norm_ahead": "off": the norm is a kernel again, the factor stays with the consumer) or
+    switch both off ("row_factor": "norm").  Portions of 300, 700 and 130 tokens of one request beside decode rows of
+    others, and a portion whose length is no multiple of anything: all three forms agree to bfloat16 roundings and
+    stay as close to float32."""
+    from purhie_b200.engine import Engine, StepEntry
+    from purhie_b200 import native
+    long = ids(1130 + 4, 901)
+    others = [ids(60 + 7 * i, 910 + i) for i in range(3)]
+    got, norm_kernels = {}, {}
+    for name, dtype, opts in (("f32", "float32", None), ("ahead", "bfloat16", None), ("kernel", "bfloat16", {"norm_ahead": "off"}),
+                              ("norm", "bfloat16", {"row_factor": "norm"})):
+        eng = Engine.from_random(SHAPES["8b"], 7, dtype=dtype, page_size=16, max_tokens=4096, max_requests=5, step_options=opts)
+        rows = []
+        for i, r in enumerate(others):
+            eng.add_request(i)
+            eng.step([StepEntry(i, r[:-3], [])])
+        eng.add_request("long")
+        rows.append(eng.step([StepEntry("long", long[:300], [0, 127, 128, 255, 256, 299])]))
+        native.lib().qe_profile_enable(1)
+        native.profile_report(True)
+        rows.append(eng.step([StepEntry("long", long[300:1000], [0, 699])] + [StepEntry(i, [r[-3]], [0]) for i, r in enumerate(others)]))
+        report = native.profile_report(True)
+        native.lib().qe_profile_enable(0)
+        norm_kernels[name] = sum(report.get(k, {"calls": 0})["calls"] for k in ("add_rmsnorm", "add_weight_sumsq"))
+        rows.append(eng.step([StepEntry(i, [r[-2]], [0]) for i, r in enumerate(others)] + [StepEntry("long", long[1000:1130], [129])]))
+        for k in range(4):
+            rows.append(eng.step([StepEntry("long", [long[1130 + k]], [0])]))
+        got[name] = np.concatenate(rows)
+        eng.close()
+    base = rel(got["norm"], got["f32"])
+    assert base < 3e-2
+    for name in ("ahead", "kernel"):
+        assert not np.isnan(got[name]).any()
+        assert rel(got[name], got["f32"]) < 1.5 * base + 2e-3, name
+        assert rel(got[name], got["norm"]) < 2e-2, name
+    assert rel(got["ahead"], got["kernel"]) < 1e-2
+    # two layers: the first layer's first norm and the norm before the head stay kernels; the other three norms do not
+    assert norm_kernels["kernel"] == 5 and norm_kernels["norm"] == 5 and norm_kernels["ahead"] == 2, norm_kernels
+
+
 def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
     """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
     8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
