@@ -591,8 +591,8 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
         !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || !(scale > 0.0f))
         return fail(PH_ERR_ARG, "attention_prefill_tc5: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
     if (head_dim != D) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: head_dim %d is not %d", head_dim, D);
-    if (page_size != 8 && page_size != 16)
-        return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: pages of %d tokens (8 or 16 are taken)", page_size);
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
+        return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: pages of %d tokens (8, 16, 32 or 64 are taken)", page_size);
     if (page_stride % D || (((uintptr_t)q | (uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)out) & 15))
         return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: tensors must be 16-byte aligned, pages whole rows");
     if (n_tiles > 65535) return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: %d tiles exceed the grid", n_tiles);
@@ -615,7 +615,7 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
         !encode(&mv, v_base, 2, kdims, kstrides, kbox))
         return fail(PH_ERR_UNSUPPORTED, "attention_prefill_tc5: cuTensorMapEncodeTiled refused the layout");
     Tc5Params p;
-    p.rows_per_page = rows_per_page; p.total_rows = (int)rows; p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : 4;
+    p.rows_per_page = rows_per_page; p.total_rows = (int)rows; p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
     p.block_table = block_table; p.table_stride = table_stride; p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len;
     p.tile_seg = tile_seg; p.tile_first = tile_first; p.n_tiles = n_tiles; p.out = (__nv_bfloat16*)out;
     p.HQ = HQ; p.HKV = HKV; p.window = window; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;

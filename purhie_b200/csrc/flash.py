@@ -77,7 +77,7 @@ def prefill(q, k_base, v_base, page_stride, page_size, block_table, seg_start, s
 
 
 def tc5_supports(head_dim: int, page_size: int) -> bool:
-    return head_dim == 128 and page_size in (8, 16)
+    return head_dim == 128 and page_size in (8, 16, 32, 64)
 
 
 def tc5_splits(n_tiles: int, num_heads: int, max_ctx: int, sms: int, window: Optional[int] = None) -> int:

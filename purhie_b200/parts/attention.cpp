@@ -14,7 +14,7 @@
 // Which kernel: float32, or a head size the tensor-core kernels do not take -> attention_generic (any size, fixed
 // order).  bfloat16 with head size 64 or 128 and groups up to 16: single-token segments go to the persistent
 // TMA-fed split-key kernel (pages of 8..64 tokens; else the cp.async one), prompt portions to the tcgen05 kernel
-// (head size 128, pages of 8 or 16) or the mma.sync tiled kernel.  The tile lists those two want are this
+// (head size 128, pages of 8 to 64) or the mma.sync tiled kernel.  The tile lists those two want are this
 // part's own metadata: prepare_step() adds them to the step.
 #include <algorithm>
 #include <cmath>
@@ -283,7 +283,7 @@ private:
         const int sms = sm_count();
         StepArray t64 = ctx.array("attention.tiles64.seg"), t64f = ctx.array("attention.tiles64.first");
         StepArray t128 = ctx.array("attention.tiles128.seg"), t128f = ctx.array("attention.tiles128.first");
-        const bool tc5_ok = head_dim_ == 128 && (cache.page_size == 8 || cache.page_size == 16) && cache.num_pages > 0;
+        const bool tc5_ok = head_dim_ == 128 && (cache.page_size == 8 || cache.page_size == 16 || cache.page_size == 32 || cache.page_size == 64) && cache.num_pages > 0;
         if (t64.count && t128.count && tc5_ok && ctx.option("prefill_kernel") != "mma_sync") {
             int splits = (int)ctx.option_int("prefill_splits");
             if (!splits) splits = tc5_splits(t128.count, heads_, ctx.prefill_max_ctx, sms, window_);

@@ -568,7 +568,7 @@ def test_attention_generic_float32_over_2500_keys():
 
 @pytest.mark.parametrize("HQ,HKV,D,page_size,window", [
     (8, 2, 128, 16, None), (4, 4, 64, 16, None), (6, 2, 64, 8, 40), (16, 1, 128, 64, 200), (32, 8, 128, 16, None),
-    (2, 1, 128, 3, 65), (4, 2, 128, 8, 150), (3, 3, 128, 16, 77)])
+    (2, 1, 128, 3, 65), (4, 2, 128, 8, 150), (3, 3, 128, 16, 77), (8, 2, 128, 32, None), (4, 1, 128, 64, None)])
 def test_attention_flash_prefill_and_decode(HQ, HKV, D, page_size, window):
     # portions that start mid-page, cross many blocks, end inside a tile; decode rows short and long
     segs = [(1, 1), (64, 64), (200, 130), (300, 1), (65, 2), (700, 1), (513, 257), (63, 1), (128, 1)]
