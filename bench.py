@@ -114,6 +114,7 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the mixed step")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="run one phase only, with few launches around it (for profiling under ncu)")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the benchmark's configuration has 16)")
     ap.add_argument("--step-options", default="", metavar="JSON",
                     help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
     ap.add_argument("--leave-out", default="", metavar="NAMES",
@@ -144,7 +145,7 @@ def main():
         args.no_points = True
     kv_tokens = max_batch * (PREFIX + 2 * (args.steps + args.warmup) + 256) + PREFILL_TOKENS + 64
     step_options = {"step": json.loads(args.step_options)} if args.step_options else {}
-    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 2, page_size=16, kv_tokens=kv_tokens, **step_options)
+    model.kv_cache_init(CONTEXT, max_sequences=max_batch + 2, page_size=args.page_size, kv_tokens=kv_tokens, **step_options)
     eng = Engine.attach(model)
     rng = np.random.default_rng(SEED)
     ids = lambda n: rng.integers(0, cfg.vocab_size, size=n).tolist()
@@ -263,7 +264,7 @@ def main():
     if args.shape == "0.6b" and not args.no_points:
         for st in streams:
             st.free()
-        model.kv_cache_init(CONTEXT, max_sequences=3, page_size=16, kv_tokens=2 * (PREFIX + 256), cuda_graphs=False)
+        model.kv_cache_init(CONTEXT, max_sequences=3, page_size=args.page_size, kv_tokens=2 * (PREFIX + 256), cuda_graphs=False)
         eng2 = Engine.attach(model)
         eng2.add_request(0)
         eng2.step([StepEntry(0, ids(PREFIX), [])])
@@ -282,7 +283,7 @@ def main():
                    "context": CONTEXT, "parallelism": "single GPU", "layers": args.layers,
                    "layers_of_config": shape["num_hidden_layers"], "hidden": E, "q_heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": D, "intermediate": FF, "vocab": V,
-                   "kv_page_tokens": 16, "kv_dtype": "bf16", "l2": f"weights ({weight_bytes / 1e9:.1f} GB) exceed L2 every step",
+                   "kv_page_tokens": args.page_size, "kv_dtype": "bf16", "l2": f"weights ({weight_bytes / 1e9:.1f} GB) exceed L2 every step",
                    "cuda_graphs": True, "prefill_tokens": PREFILL_TOKENS, "sampling": "greedy, inside the timed step"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
