@@ -105,14 +105,15 @@ CacheManager::CacheManager(std::vector<CacheNeed> needs, int page_size, std::vec
         throw Error(kInvalidArg, std::to_string(num_pages.size()) + " page counts for " + std::to_string(groups_.size()) + " groups");
     for (size_t i = 0; i < groups_.size(); i++) {
         groups_[i].allocator = PageAllocator(num_pages[i]);
-        groups_[i].page_stride = (long long)groups_[i].entries.size() * groups_[i].kv_heads * page_size_ * (groups_[i].head_dim + groups_[i].value_dim);
+        // one entry's keys and values of one page; an entry's pages lie side by side, the entries one after the other
+        groups_[i].page_stride = (long long)groups_[i].kv_heads * page_size_ * (groups_[i].head_dim + groups_[i].value_dim);
     }
 }
 
 void CacheManager::materialize(DType dtype, bool poison, cudaStream_t stream) {
     dtype_ = dtype; poison_ = poison; stream_ = stream;
     for (PageGroup& g : groups_) {
-        size_t bytes = (size_t)g.allocator.num_pages() * (size_t)g.page_stride * dtype_size(dtype);
+        size_t bytes = g.entries.size() * (size_t)g.allocator.num_pages() * (size_t)g.page_stride * dtype_size(dtype);
         g.pool = DeviceBuffer(std::max<size_t>(bytes, 16));
         // all bits set is a NaN in float32 and in bfloat16
         QE_CUDA(cudaMemsetAsync(g.pool.data(), poison ? 0xFF : 0, g.pool.bytes(), stream));
@@ -271,9 +272,11 @@ void CacheManager::release(int64_t id) {
 void CacheManager::free_pages_of(PageGroup& g, const std::vector<int>& pages) {
     std::vector<int> released = g.allocator.free(pages);
     if (poison_ && materialized_) {
+        // the page of every entry of the group: rows of a 2-D fill, one entry's region apart
         const size_t bytes = (size_t)g.page_stride * dtype_size(dtype_);
+        const size_t entry_bytes = (size_t)g.allocator.num_pages() * bytes;
         for (int p : released)
-            QE_CUDA(cudaMemsetAsync(static_cast<char*>(g.pool.data()) + (size_t)p * bytes, 0xFF, bytes, stream_));
+            QE_CUDA(cudaMemset2DAsync(static_cast<char*>(g.pool.data()) + (size_t)p * bytes, entry_bytes, 0xFF, bytes, g.entries.size(), stream_));
     }
 }
 
@@ -308,8 +311,9 @@ CacheView CacheManager::view(int entry, int owner) const {
         const size_t v_elems = (size_t)g.kv_heads * page_size_ * g.value_dim;   // ... and of its values
         char* base = static_cast<char*>(g.pool.data());
         v.group = g.index;
-        v.k_base = base + ((size_t)slot * (k_elems + v_elems)) * elem;
-        v.v_base = base + ((size_t)slot * (k_elems + v_elems) + k_elems) * elem;
+        const size_t entry_elems = (size_t)g.allocator.num_pages() * (k_elems + v_elems);   // all pages of one entry
+        v.k_base = base + ((size_t)slot * entry_elems) * elem;
+        v.v_base = base + ((size_t)slot * entry_elems + k_elems) * elem;
         v.kv_heads = g.kv_heads; v.key_dim = g.head_dim; v.value_dim = g.value_dim;
         v.kv_dtype = dtype_;
         v.page_stride = g.page_stride;

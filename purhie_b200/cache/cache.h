@@ -62,8 +62,11 @@ struct PageGroup {
     int kv_heads = 0, head_dim = 0, value_dim = 0, window = 0;      // value_dim: as CacheNeed::v_dim()
     std::vector<int> entries;                      // run-order entries whose keys and values live in this group
     PageAllocator allocator;
-    DeviceBuffer pool;                             // [pages, entries, {K: kv_heads x page_size x head_dim, V: ... x value_dim}]
-    long long page_stride = 0;                     // elements per page
+    // [entries, pages, {K: kv_heads x page_size x head_dim, V: ... x value_dim}]: what one layer's attention reads lies
+    // together (a pool of tens of GB with the layers interleaved page by page spreads every layer over all of it,
+    // and the address translations of a layer's pages stop fitting the translation caches)
+    DeviceBuffer pool;
+    long long page_stride = 0;                     // elements of one entry's page (keys and values)
     int entry_slot(int entry) const;
 };
 

@@ -57,14 +57,15 @@ def test_groups_are_formed_by_geometry_and_policy():
 
 def test_values_narrower_than_keys_get_a_group_and_pages_of_their_own_size():
     """A mixer may keep values that are not as wide as its keys (compressed values): such entries form a group of
-    their own, and a page of that group holds kv_heads x page_size x (key width + value width) elements per entry."""
+    their own, and a page of that group holds kv_heads x page_size x (key width + value width) elements per entry
+    (`page_stride`: an entry's pages lie side by side, the entries of a group one after the other)."""
     needs = [CacheNeed.pages(2, 16), CacheNeed.pages(2, 16, value_dim=4), CacheNeed.pages(2, 16, value_dim=4),
              CacheNeed.pages(2, 16, value_dim=16)]
     m = CacheManager(needs, page_size=8, num_pages=[5, 7], max_requests=2)
     groups = m.info()["groups"]
     assert [(g["entries"], g["head_dim"], g["value_dim"]) for g in groups] == [([0, 3], 16, 16), ([1, 2], 16, 4)]
-    assert groups[0]["page_stride"] == 2 * (2 * 8 * (16 + 16))
-    assert groups[1]["page_stride"] == 2 * (2 * 8 * (16 + 4))
+    assert groups[0]["page_stride"] == 2 * 8 * (16 + 16)
+    assert groups[1]["page_stride"] == 2 * 8 * (16 + 4)
     m.add_request("a")
     m.reserve("a", 20)
     m.advance("a", 20)
