@@ -72,9 +72,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swapped: bool, 
     ``swiglu`` the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up.  ``accumulate``
     (plain orientation, float32, one split): out += the product.  ``row_sumsq`` [M, chunks] (swapped with bfloat16
     out, or plain with block_n 256): the rows of x lack the factor rsqrt(sum(row_sumsq[m]) / row_width + row_eps);
-    the epilogue applies it.  ``norm_ahead`` (weight float32 [N], rows bfloat16 [M, N], sumsq float32 [M, ceil(N / 256)];
+    the epilogue applies it.  ``norm_ahead`` (weight float32 [N], rows bfloat16 [M, N], sumsq float32 [M, 2 * ceil(N / 256)];
     plain, block_n 256, accumulate): rows = (the new out) * weight, sumsq[m, j] = the sum of squares of the new out
-    over the columns of tile j."""
+    over columns 128 j .. 128 j + 127."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"gemm_tcgen05: {name} must be a contiguous bfloat16 CUDA tensor")
@@ -93,7 +93,7 @@ def _norm_ahead_pointers(norm_ahead, M: int, N: int):
     if norm_ahead is None:
         return None, None, None
     weight, rows, sumsq = norm_ahead
-    tiles = (N + 255) // 256
+    tiles = 2 * ((N + 255) // 256)
     if (weight.dtype != torch.float32 or weight.numel() != N or rows.dtype != torch.bfloat16 or rows.numel() != M * N
             or sumsq.dtype != torch.float32 or sumsq.numel() != M * tiles
             or not (weight.is_contiguous() and rows.is_contiguous() and sumsq.is_contiguous())):

@@ -61,8 +61,8 @@ struct GemmParams {
     float row_eps;
     // Plain orientation with accumulate, tiles of 256 columns: what the norm after this addition would do is done here.
     // Beside out += product, the new rows times norm_weight go to norm_rows (bfloat16, [rows_a, ld]) and each row's sum
-    // of squares over this tile's columns to norm_sumsq[row][tile] ([rows_a, b_tiles]): the rows lack the factor
-    // rsqrt(sum over the tiles / ld + eps), which their consumer applies (row_sumsq above).  Null: none.
+    // of squares over 128 columns to norm_sumsq[row][column / 128] ([rows_a, 2 * b_tiles]): the rows lack the factor
+    // rsqrt(sum over the entries / ld + eps), which their consumer applies (row_sumsq above).  Null: none.
     const float* norm_weight;
     __nv_bfloat16* norm_rows;
     float* norm_sumsq;
@@ -360,8 +360,9 @@ __device__ __forceinline__ void store_chunk_accumulate_staged(const GemmParams& 
     __syncwarp();                                                    // the buffer is written again for the next chunk
 }
 
-// After the last chunk of a tile: the sums of squares of the warp's rows over the tile's columns, to norm_sumsq.
-__device__ __forceinline__ void store_tile_sumsq(const GemmParams& p, float* ss, int row0, int lane, int tile_b) {
+// The sums of squares of the warp's rows over 128 columns (half of a tile's), to norm_sumsq[row][half_index]; a row has
+// two entries per tile.
+__device__ __forceinline__ void store_tile_sumsq(const GemmParams& p, float* ss, int row0, int lane, int half_index) {
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
         float s = ss[it];
@@ -369,7 +370,8 @@ __device__ __forceinline__ void store_tile_sumsq(const GemmParams& p, float* ss,
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
         const int a = row0 + it * 4 + (lane >> 3);
-        if ((lane & 7) == 0 && a < p.rows_a) p.norm_sumsq[(size_t)a * p.b_tiles + tile_b] = s;
+        if ((lane & 7) == 0 && a < p.rows_a) p.norm_sumsq[(size_t)a * (2 * p.b_tiles) + half_index] = s;
+        ss[it] = 0.0f;
     }
 }
 
@@ -624,12 +626,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 else if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
                 else if (ROW_OPS && staged_add) {
-                    if constexpr (ROW_OPS) store_chunk_accumulate_staged(p, r, old, vectors, (float*)staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                    if constexpr (ROW_OPS) {
+                        store_chunk_accumulate_staged(p, r, old, vectors, (float*)staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                        if (p.norm_sumsq && ((c + CH) & 127) == 0) store_tile_sumsq(p, ss, a0 + q * 32, lane, 2 * (b0 / BN) + (c >> 7));
+                    }
                 }
                 else store_chunk<CH>(p, r, a, b0, c, split_off);
-            }
-            if constexpr (ROW_OPS) {
-                if (!p.swapped && p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, b0 / BN);
             }
             tc_fence_before();
             __syncwarp();
@@ -667,7 +669,9 @@ constexpr int PAIR_B_BYTES = PAIR_HALF * BK * 2;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_TMEM_COLS = 2 * PAIR_BN;
-constexpr int PAIR_STAGING_BYTES = 4 * 32 * 32 * 4;        // per epilogue warp: 32 rows x 32 columns, float32
+constexpr int PAIR_EPILOGUE_WARPS = 8;             // two per quarter of the accumulator's rows, 128 columns each
+constexpr int PAIR_THREADS = 64 + 32 * PAIR_EPILOGUE_WARPS;
+constexpr int PAIR_STAGING_BYTES = PAIR_EPILOGUE_WARPS * 32 * 32 * 4;        // per epilogue warp: 32 rows x 32 columns, float32
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_STAGING_BYTES;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -706,7 +710,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int STAGES = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -718,14 +722,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-    float* staging = (float*)(smem + STAGES * PAIR_STAGE_BYTES + 256);       // [4 warps][32 x 32]
+    float* staging = (float*)(smem + STAGES * PAIR_STAGE_BYTES + 256);       // [epilogue warps][32 x 32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2 * PAIR_EPILOGUE_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -807,7 +811,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
         }
     } else {
-        const int q = warp & 3;
+        // eight epilogue warps: warp w may read the 32 accumulator rows of quarter w % 4; the two warps of a quarter
+        // take 128 columns each, so that the epilogue nothing hides (the last round's) is half as long
+        const int q = warp & 3, half = (warp - 2) >> 2, c_first = half * (PAIR_BN / 2);
         pdl_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -819,7 +825,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // out += product: the values added to are fetched one chunk ahead, the first while the products still run
             const bool vectors = p.accumulate && accumulate_in_vectors(p);
             float4 old[8], old_next[8];
-            if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, 0, old_next);
+            if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c_first, old_next);
             if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
             tc_fence_after();
             const int a = a0 + q * 32 + lane;
@@ -828,23 +834,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
             float ss[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
-            for (int c = 0; c < PAIR_BN; c += 32) {
+            for (int c = c_first; c < c_first + PAIR_BN / 2; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 if (vectors) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) old[i] = old_next[i];
-                    if (c + 32 < PAIR_BN) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + 32, old_next);
+                    if (c + 32 < c_first + PAIR_BN / 2) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + 32, old_next);
                 }
                 tmem_ld_wait();
                 if (scale_row) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_f);
                 }
-                if (p.accumulate) store_chunk_accumulate_staged(p, r, old, vectors, staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                if (p.accumulate) store_chunk_accumulate_staged(p, r, old, vectors, staging + (warp - 2) * 32 * 32, a0 + q * 32, lane, b0, c, ss);
                 else store_chunk<32>(p, r, a, b0, c, split_off);
             }
-            if (p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, b0 / PAIR_BN);
+            if (p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, 2 * (b0 / PAIR_BN) + half);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
@@ -949,7 +955,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
     if (work < clusters) clusters = work;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * clusters);
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(PAIR_THREADS);
     cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
     cfg.stream = stream;
     // The cluster kernel is launched in plain stream order, not as a programmatic dependent: started early, under a
@@ -988,7 +994,7 @@ const char* row_ops_refused(const float* row_sumsq, int row_chunks, int row_widt
 // float32 partial results [splits][M, N] with splits > 1.  max_clusters: 0 or a cap on the number of CTA pairs.
 // accumulate: out (float32, one split, no activation) += the product.
 // row_sumsq .. row_eps: the factor per token that the activations lack (one split, no accumulate); norm_weight [N],
-// norm_rows (bfloat16 [M, N]), norm_sumsq (float32 [M, ceil(N / 256)]): with accumulate, what the norm after this
+// norm_rows (bfloat16 [M, N]), norm_sumsq (float32 [M, 2 * ceil(N / 256)]): with accumulate, what the norm after this
 // addition needs (GemmParams).  All may be null.
 PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
                                         int splits, int max_clusters, int swiglu, int accumulate,

@@ -137,8 +137,8 @@ Addend Linear::operator()(const Tensor& x_in, StepContext& ctx, const std::strin
         void* ahead_rows = nullptr;
         float* ahead_sumsq = nullptr;
         if (work_ahead) {
-            // the norm behind this addition: its weighted rows and their sums of squares per tile of 256 features
-            const int tiles = ceil_div(N, 256);
+            // the norm behind this addition: its weighted rows and their sums of squares per 128 features (two per tile)
+            const int tiles = 2 * ceil_div(N, 256);
             work_ahead->rows = ws.get("norm_ahead_rows", {M, N}, DType::BF16);
             Tensor sums = ws.get("norm_ahead_sumsq", {M, tiles}, DType::F32);
             work_ahead->scale.sumsq = sums.as<float>(); work_ahead->scale.chunks = tiles;

@@ -228,14 +228,14 @@ def test_gemm_tcgen05_with_many_rows_does_the_work_of_the_norms_around_it(M, N, 
         run(plain, accumulate=True)
         out = base.clone()
         rows = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-        sumsq = torch.full((M, tiles), float("nan"), device=DEV)
+        sumsq = torch.full((M, 2 * tiles), float("nan"), device=DEV)            # per 128 columns: two entries per tile
         run(out, accumulate=True, norm_ahead=(wn, rows, sumsq))
         gemm100.check_errors(DEV)
         assert torch.equal(out, plain)
         assert torch.equal(rows, (out * wn).to(torch.bfloat16))
         padded = torch.zeros(M, tiles * 256, dtype=torch.float64, device=DEV)
         padded[:, :N] = out.double() ** 2
-        assert rel(sumsq, padded.view(M, tiles, 256).sum(-1)) < 1e-6
+        assert rel(sumsq, padded.view(M, 2 * tiles, 128).sum(-1)) < 1e-6
         want = prod * factor
         o32 = torch.full((M, N), float("nan"), device=DEV)
         run(o32, row_sumsq=sq, row_width=width, row_eps=eps)
@@ -255,7 +255,7 @@ def test_gemm_tcgen05_refuses_row_work_it_cannot_do():
     from purhie_b200.csrc.ops import KernelError
     x, w = rnd(128, 64, dtype=torch.bfloat16), rnd(256, 64, dtype=torch.bfloat16)
     out = torch.zeros(128, 256, device=DEV)
-    ahead = (torch.ones(256, device=DEV), torch.empty(128, 256, dtype=torch.bfloat16, device=DEV), torch.empty(128, 1, device=DEV))
+    ahead = (torch.ones(256, device=DEV), torch.empty(128, 256, dtype=torch.bfloat16, device=DEV), torch.empty(128, 2, device=DEV))
     sq = torch.ones(128, 2, device=DEV)
     with pytest.raises(KernelError, match="together with the addition"):
         gemm100.gemm_pair(x, w, out, norm_ahead=ahead)                                    # not adding into the output
