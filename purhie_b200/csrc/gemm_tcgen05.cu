@@ -584,17 +584,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     factor[i] = rsqrtf(s / (float)p.row_width + p.row_eps);
                 }
             }
-            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
-            tc_fence_after();
+            // plain orientation, tiles of 256 columns: the factor of this thread's row (fetched while the products run), and
+            // its sum of squares for the norm ahead
             const int a = a0 + q * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-            const size_t split_off = (size_t)split * (size_t)p.split_stride;
-            // plain orientation, tiles of 256 columns: the factor of this thread's row, and its sum of squares for the norm ahead
             constexpr bool ROW_OPS = BN == 256;
             const bool scale_row = ROW_OPS && !p.swapped && p.row_sumsq != nullptr;
             float row_f = 1.0f;
             float ss[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             if constexpr (ROW_OPS) row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
+            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const size_t split_off = (size_t)split * (size_t)p.split_stride;
             // out += product (tiles of 256 columns): the values added to are fetched one chunk ahead
             const bool staged_add = ROW_OPS && !p.swapped && p.accumulate;
             const bool vectors = staged_add && accumulate_in_vectors(p);
@@ -826,12 +827,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const bool vectors = p.accumulate && accumulate_in_vectors(p);
             float4 old[8], old_next[8];
             if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c_first, old_next);
-            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
-            tc_fence_after();
+            // ... and so is the factor of this thread's row
             const int a = a0 + q * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PAIR_BN);
             const bool scale_row = p.row_sumsq != nullptr;
             const float row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
+            if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PAIR_BN);
             float ss[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
             for (int c = c_first; c < c_first + PAIR_BN / 2; c += 32) {
