@@ -66,6 +66,9 @@ struct GemmParams {
     const float* norm_weight;
     __nv_bfloat16* norm_rows;
     float* norm_sumsq;
+    // Pair kernel, bfloat16 output of whole sums (plain or with the activation): the epilogue leaves boxes of 32 rows x
+    // 64 columns in shared memory and the copy engine stores them (whole lines, nothing for the warps to wait for).
+    int tma_store;
     int* error_flag;
 };
 
@@ -315,14 +318,18 @@ __device__ __forceinline__ void load_accumulate_chunk(const GemmParams& p, int r
 // r: this lane's accumulator row; old: what load_accumulate_chunk fetched for this chunk (vector form only).
 // With the norm ahead, the new rows times the norm's weight go to norm_rows, and ss[it] gathers this lane's share of
 // the sum of squares of row 4 it + lane / 8.  Every lane of the warp calls this.
+// next_c >= 0 (vector form): once the accumulator chunk is in shared memory and its registers are free, the values
+// that chunk next_c is added to are asked for, into old_next.
 __device__ __forceinline__ void store_chunk_accumulate_staged(const GemmParams& p, const uint32_t* r, const float4* old, bool vectors,
-                                                              float* buf, int row0, int lane, int b0, int c, float* ss) {
+                                                              float* buf, int row0, int lane, int b0, int c, float* ss,
+                                                              float4* old_next, int next_c) {
     float4* mine = (float4*)(buf + lane * 32);
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         mine[j ^ (lane & 7)] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                                            __uint_as_float(r[4 * j + 3]));
     __syncwarp();
+    if (vectors && next_c >= 0) load_accumulate_chunk(p, row0, lane, b0, next_c, old_next);
     const int sub = lane >> 3, slot = lane & 7;
     const int col = b0 + c + slot * 4;                               // first of this lane's four columns
     const bool ahead = p.norm_weight != nullptr;
@@ -604,14 +611,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
             for (int c = 0; c < BN; c += CH) {
                 uint32_t r[CH];
-                if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 if constexpr (ROW_OPS) {
                     if (vectors) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) old[i] = old_next[i];
-                        if (c + CH < BN) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + CH, old_next);
                     }
                 }
+                if constexpr (CH == 32) tmem_ld32(taddr + c, r); else tmem_ld16(taddr + c, r);
                 tmem_ld_wait();
                 if constexpr (ROW_OPS) {
                     if (scale_row) {
@@ -628,7 +634,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 else if (p.swapped && p.swiglu) store_chunk_swapped_swiglu<CH>(p, r, a, b0, c);
                 else if (ROW_OPS && staged_add) {
                     if constexpr (ROW_OPS) {
-                        store_chunk_accumulate_staged(p, r, old, vectors, (float*)staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                        store_chunk_accumulate_staged(p, r, old, vectors, (float*)staging + q * 32 * 32, a0 + q * 32, lane, b0, c, ss,
+                                                      old_next, c + CH < BN ? c + CH : -1);
                         if (p.norm_sumsq && ((c + CH) & 127) == 0) store_tile_sumsq(p, ss, a0 + q * 32, lane, 2 * (b0 / BN) + (c >> 7));
                     }
                 }
@@ -698,6 +705,28 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c_inner), "r"(c_row) : "memory");
 }
+// A box from shared memory to its place in the output; the calling thread's bulk group tracks it.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c_inner, int c_row) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c_inner), "r"(c_row) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Eight bfloat16 values as one 16-byte chunk of row `lane` of a 32 x 64 box laid out as the copy engine's 128-byte
+// swizzle wants it (chunk ^ (row & 7)).
+__device__ __forceinline__ void put_chunk(unsigned char* box, int lane, int chunk, float v0, float v1, float v2, float v3,
+                                          float v4, float v5, float v6, float v7) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v0, v1), b = __floats2bfloat162_rn(v2, v3);
+    const __nv_bfloat162 c = __floats2bfloat162_rn(v4, v5), d = __floats2bfloat162_rn(v6, v7);
+    *(uint4*)(box + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+        make_uint4(*(const uint32_t*)&a, *(const uint32_t*)&b, *(const uint32_t*)&c, *(const uint32_t*)&d);
+}
+__device__ __forceinline__ float silu_times(uint32_t g_bits, uint32_t u_bits, float f) {
+    const float g = __uint_as_float(g_bits) * f, u = __uint_as_float(u_bits) * f;
+    return g / (1.0f + __expf(-g)) * u;
+}
 __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n.reg .pred p;\n"
@@ -711,19 +740,22 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 
+// ADDS: the instance for out += product (its epilogue keeps two chunks of out in registers); the other instance stores.
+template <bool ADDS>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_out, GemmParams p) {
     constexpr int STAGES = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_BYTES;
-    uint64_t* full = (uint64_t*)(smem + STAGES * PAIR_STAGE_BYTES);
+    float* staging = (float*)(smem + STAGES * PAIR_STAGE_BYTES);             // [epilogue warps][4 KB], 1024-byte aligned
+    uint64_t* full = (uint64_t*)(smem + STAGES * PAIR_STAGE_BYTES + PAIR_STAGING_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-    float* staging = (float*)(smem + STAGES * PAIR_STAGE_BYTES + 256);       // [epilogue warps][32 x 32]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -823,13 +855,62 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const int tile = w / p.splits;
             const int a0 = (tile % a_tiles) * 2 * BM + (int)rank * BM, b0 = (tile / a_tiles) * PAIR_BN;
             const size_t split_off = (size_t)(w % p.splits) * (size_t)p.split_stride;
+            if (!ADDS && p.tma_store) {
+                const int a = a0 + q * 32 + lane;
+                const float row_f = p.row_sumsq != nullptr ? plain_row_factor(p, a) : 1.0f;   // fetched while the products run
+                if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PAIR_BN);
+                // bfloat16 out: the warp's 32 rows x 128 accumulator columns leave as boxes of 64 output columns that
+                // the copy engine stores (two boxes, or one with the activation); rows and columns outside of out are
+                // clipped by the copy
+                unsigned char* box = (unsigned char*)(staging + (warp - 2) * 32 * 32);
+                const int row0 = a0 + q * 32;
+                const int boxes = p.swiglu ? 1 : 2, per_box = p.swiglu ? 4 : 2;       // chunks of 32 accumulator columns per box
+#pragma unroll 1
+                for (int b = 0; b < boxes; ++b) {
+                    if (lane == 0) tma_store_wait_read();                          // the box before this one has left shared memory
+                    __syncwarp();
+#pragma unroll 1
+                    for (int k = 0; k < per_box; ++k) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c_first + (b * per_box + k) * 32, r);
+                        tmem_ld_wait();
+                        if (p.swiglu) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                put_chunk(box, lane, 2 * k + j,
+                                          silu_times(r[16 * j], r[16 * j + 1], row_f), silu_times(r[16 * j + 2], r[16 * j + 3], row_f),
+                                          silu_times(r[16 * j + 4], r[16 * j + 5], row_f), silu_times(r[16 * j + 6], r[16 * j + 7], row_f),
+                                          silu_times(r[16 * j + 8], r[16 * j + 9], row_f), silu_times(r[16 * j + 10], r[16 * j + 11], row_f),
+                                          silu_times(r[16 * j + 12], r[16 * j + 13], row_f), silu_times(r[16 * j + 14], r[16 * j + 15], row_f));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                put_chunk(box, lane, 4 * k + j, __uint_as_float(r[8 * j]) * row_f, __uint_as_float(r[8 * j + 1]) * row_f,
+                                          __uint_as_float(r[8 * j + 2]) * row_f, __uint_as_float(r[8 * j + 3]) * row_f,
+                                          __uint_as_float(r[8 * j + 4]) * row_f, __uint_as_float(r[8 * j + 5]) * row_f,
+                                          __uint_as_float(r[8 * j + 6]) * row_f, __uint_as_float(r[8 * j + 7]) * row_f);
+                        }
+                    }
+                    fence_async_shared();
+                    __syncwarp();
+                    const int col0 = p.swiglu ? (b0 + c_first) >> 1 : b0 + c_first + b * 64;
+                    if (lane == 0 && row0 < p.rows_a && col0 < (int)p.ld) tma_store_2d(&map_out, box, col0, row0);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                continue;
+            }
             // out += product: the values added to are fetched one chunk ahead, the first while the products still run
-            const bool vectors = p.accumulate && accumulate_in_vectors(p);
-            float4 old[8], old_next[8];
-            if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c_first, old_next);
+            const bool vectors = ADDS && accumulate_in_vectors(p);
+            float4 old[ADDS ? 8 : 1], old_next[ADDS ? 8 : 1];
+            if constexpr (ADDS) { if (vectors) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c_first, old_next); }
             // ... and so is the factor of this thread's row
             const int a = a0 + q * 32 + lane;
-            const bool scale_row = p.row_sumsq != nullptr;
+            const bool scale_row = !ADDS && p.row_sumsq != nullptr;       // a product that adds takes finished rows
             const float row_f = scale_row ? plain_row_factor(p, a) : 1.0f;
             if (!mbar_wait(&acc_full[acc], acc_phase, p.error_flag, PH_ERR_WAIT_EPILOGUE)) { ok = false; break; }
             tc_fence_after();
@@ -838,26 +919,31 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll 1
             for (int c = c_first; c < c_first + PAIR_BN / 2; c += 32) {
                 uint32_t r[32];
+                if constexpr (ADDS) {
+                    if (vectors) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) old[i] = old_next[i];
+                    }
+                }
                 tmem_ld32(taddr + c, r);
-                if (vectors) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) old[i] = old_next[i];
-                    if (c + 32 < c_first + PAIR_BN / 2) load_accumulate_chunk(p, a0 + q * 32, lane, b0, c + 32, old_next);
-                }
                 tmem_ld_wait();
-                if (scale_row) {
+                if constexpr (!ADDS) {
+                    if (scale_row) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_f);
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_f);
+                    }
                 }
-                if (p.accumulate) store_chunk_accumulate_staged(p, r, old, vectors, staging + (warp - 2) * 32 * 32, a0 + q * 32, lane, b0, c, ss);
+                if constexpr (ADDS) store_chunk_accumulate_staged(p, r, old, vectors, staging + (warp - 2) * 32 * 32, a0 + q * 32, lane, b0, c, ss,
+                                                                  old_next, c + 32 < c_first + PAIR_BN / 2 ? c + 32 : -1);
                 else store_chunk<32>(p, r, a, b0, c, split_off);
             }
-            if (p.accumulate && p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, 2 * (b0 / PAIR_BN) + half);
+            if constexpr (ADDS) { if (p.norm_sumsq) store_tile_sumsq(p, ss, a0 + q * 32, lane, 2 * (b0 / PAIR_BN) + half); }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (!ADDS && p.tma_store && lane == 0) tma_store_wait_all();      // the stores of this thread are done before the CTA ends
     }
     tc_fence_before();
     __syncthreads();
@@ -944,10 +1030,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     return check_launch("gemm_tcgen05");
 }
 
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_clusters, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& p, int max_clusters,
+                cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess)
             return fail(PH_ERR_LAUNCH, "gemm_tcgen05_pair: cannot reserve %d bytes of shared memory", PAIR_SMEM_BYTES);
         configured = true;
     }
@@ -969,7 +1057,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, ma, mb, p) != cudaSuccess) {}
+    if (p.accumulate) { if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<true>, ma, mb, mo, p) != cudaSuccess) {} }
+    else if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<false>, ma, mb, mo, p) != cudaSuccess) {}
     return check_launch("gemm_tcgen05_pair");
 }
 
@@ -1025,7 +1114,13 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
-    return launch_pair(ma, mb, p, max_clusters, stream);
+    // bfloat16 results of whole sums leave through the copy engine where its rules allow (rows of a multiple of 16 bytes)
+    CUtensorMap mo = ma;
+    p.tma_store = 0;
+    if (out_dtype == PH_BF16 && splits == 1 && !accumulate && p.ld % 8 == 0 && (((uintptr_t)out) & 15) == 0 &&
+        make_map(&mo, out, M, (int)p.ld, 32))
+        p.tma_store = 1;
+    return launch_pair(ma, mb, mo, p, max_clusters, stream);
 }
 
 // out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
@@ -1077,6 +1172,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
+    p.tma_store = 0;
     switch (block_n) {
         case 16: return launch<16>(ma, mb, p, max_ctas, stream);
         case 32: return launch<32>(ma, mb, p, max_ctas, stream);
