@@ -66,8 +66,10 @@ struct GemmParams {
     const float* norm_weight;
     __nv_bfloat16* norm_rows;
     float* norm_sumsq;
-    // Pair kernel, bfloat16 output of whole sums (plain or with the activation): the epilogue leaves boxes of 32 rows x
-    // 64 columns in shared memory and the copy engine stores them (whole lines, nothing for the warps to wait for).
+    // Pair kernel, results that are stored, not added: the epilogue leaves boxes of 32 rows x 128 bytes in shared memory
+    // and the copy engine stores them (whole lines, nothing for the warps to wait for).  1: bfloat16 output of whole
+    // sums (plain or with the activation), boxes of 64 columns; 2: float32 (whole or partial sums), boxes of 32 columns
+    // of out seen as [splits][rows][columns].  0: the warps store.
     int tma_store;
     int* error_flag;
 };
@@ -711,6 +713,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                  ::"l"(map), "r"(smem_u32(src)), "r"(c_inner), "r"(c_row) : "memory");
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c_inner, int c_row, int c_outer) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(c_inner), "r"(c_row), "r"(c_outer) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -866,6 +873,30 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 // clipped by the copy
                 unsigned char* box = (unsigned char*)(staging + (warp - 2) * 32 * 32);
                 const int row0 = a0 + q * 32;
+                if (p.tma_store == 2) {
+                    // float32: every chunk of 32 accumulator columns is a box
+#pragma unroll 1
+                    for (int c = c_first; c < c_first + PAIR_BN / 2; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c, r);
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *(float4*)(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                                make_float4(__uint_as_float(r[4 * j]) * row_f, __uint_as_float(r[4 * j + 1]) * row_f,
+                                            __uint_as_float(r[4 * j + 2]) * row_f, __uint_as_float(r[4 * j + 3]) * row_f);
+                        fence_async_shared();
+                        __syncwarp();
+                        if (lane == 0 && row0 < p.rows_a && b0 + c < p.rows_b) tma_store_3d(&map_out, box, b0 + c, row0, w % p.splits);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[acc], 0));
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                    continue;
+                }
                 const int boxes = p.swiglu ? 1 : 2, per_box = p.swiglu ? 4 : 2;       // chunks of 32 accumulator columns per box
 #pragma unroll 1
                 for (int b = 0; b < boxes; ++b) {
@@ -999,6 +1030,31 @@ bool make_map(CUtensorMap* out, const void* ptr, int rows, int K, int box_rows) 
     return true;
 }
 
+// out as float32 [splits][rows][cols] seen as boxes of 32 rows x 32 columns of one split, 128-byte swizzle.
+bool make_map_f32_out(CUtensorMap* out, const void* ptr, int rows, int cols, int splits) {
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+    const auto key = std::make_tuple(ptr, rows, cols, splits);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)splits};
+    const cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)rows * (cuuint64_t)cols * 4};
+    const cuuint32_t box[3] = {32, 32, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return true;
+}
+
 int sm_count() {
     static int n = 0;
     if (!n) {
@@ -1120,6 +1176,9 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     if (out_dtype == PH_BF16 && splits == 1 && !accumulate && p.ld % 8 == 0 && (((uintptr_t)out) & 15) == 0 &&
         make_map(&mo, out, M, (int)p.ld, 32))
         p.tma_store = 1;
+    else if (out_dtype == PH_F32 && !accumulate && !swiglu && N % 4 == 0 && (((uintptr_t)out) & 15) == 0 &&
+             make_map_f32_out(&mo, out, M, N, splits))
+        p.tma_store = 2;
     return launch_pair(ma, mb, mo, p, max_clusters, stream);
 }
 
