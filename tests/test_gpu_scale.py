@@ -255,6 +255,44 @@ def test_the_norm_done_in_the_epilogue_of_the_product_in_front_gives_what_its_ow
     assert norm_kernels["kernel"] == 5 and norm_kernels["norm"] == 5 and norm_kernels["ahead"] == 2, norm_kernels
 
 
+def test_a_sliding_window_layer_at_real_layer_sizes():
+    """Two 8B-class layers, the second with a window of 1,000 keys: a 3,000-token prompt whole and in portions of 700,
+    each followed by 20 decoded tokens.  float32 gives the same bits either way (places at the window's edge among the
+    wanted ones); bfloat16 stays as close to float32 as without a window; the window group gives back the pages the
+    window has passed."""
+    from purhie_b200.engine import Engine, StepEntry
+    shape = dict(SHAPES["8b"], use_sliding_window=True, sliding_window=1000, max_window_layers=1,
+                 layer_types=["full_attention", "sliding_attention"])
+    toks = ids(3020, 31)
+    wanted = (999, 1000, 1001, 2999)
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(shape, 7, dtype=dtype, page_size=16, max_tokens=3 * 3200, max_requests=3)
+        res = {}
+        eng.add_request("w")
+        res["whole"] = eng.step([StepEntry("w", toks[:3000], list(wanted))])
+        res["decode"] = np.concatenate([eng.step([StepEntry("w", [toks[3000 + k]], [0])]) for k in range(20)])
+        eng.add_request("c")
+        rows = []
+        for s in range(0, 3000, 700):
+            part = toks[s:min(s + 700, 3000)]
+            want = [i - s for i in wanted if s <= i < s + len(part)]
+            r = eng.step([StepEntry("c", part, want)])
+            if want:
+                rows.append(r)
+        res["chunks"] = np.concatenate(rows)
+        res["decode_after_chunks"] = np.concatenate([eng.step([StepEntry("c", [toks[3000 + k]], [0])]) for k in range(20)])
+        free = eng.info()["free_pages"]
+        assert free[1] > free[0] + 200                     # two requests of 3,020 tokens: the window group holds 1,000 of each
+        out[dtype] = res
+        eng.close()
+    f32, b16 = out["float32"], out["bfloat16"]
+    assert np.array_equal(f32["whole"], f32["chunks"]) and np.array_equal(f32["decode"], f32["decode_after_chunks"])
+    for name in f32:
+        assert not np.isnan(b16[name]).any()
+        assert rel(b16[name], f32[name]) < 3e-2, name
+
+
 def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
     """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
     8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
