@@ -108,6 +108,7 @@ _SIGNATURES = {
                                  c_void_p],
         "ph_gemm_simple": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ph_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
+        "ph_argmax_parts": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p],
         "ph_sample_temperature": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
         "ph_sample_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     },
@@ -306,11 +307,16 @@ def gemm_simple(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     return out
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy choice per row, the lowest id on ties.  With ``scratch`` (bytes: rows x (4 + 64 x 8), the first 4 x rows
+    zero before the first call) several CTAs share a row."""
     _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
     V = logits.shape[-1]
     R = logits.numel() // V
-    call("core", "ph_argmax", _ptr(logits), R, V, _ptr(out), _stream())
+    if scratch is None:
+        call("core", "ph_argmax", _ptr(logits), R, V, _ptr(out), _stream())
+    else:
+        call("core", "ph_argmax_parts", _ptr(logits), R, V, _ptr(out), _ptr(scratch), scratch.numel() * scratch.element_size(), _stream())
     return out
 
 

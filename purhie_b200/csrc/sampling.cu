@@ -26,11 +26,31 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ lo
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += NT) {
-        const float v = row[i];
-        if (idx == 0x7fffffff || v > best) { best = v; idx = i; }   // i ascends: a tie keeps the lower id
-    }
     auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
+    int done = 0;
+    if ((((uintptr_t)row) & 15) == 0) {
+        // four values per load, four loads in flight per thread: one CTA reads a row of 150,000 logits, and how many
+        // bytes it has under way decides how long that takes
+        const float4* row4 = (const float4*)row;
+        const int n4 = V >> 2;
+        auto take = [&](const float4& q, int i) {                      // ids ascend inside a vector: a tie keeps the lower id
+            if (idx == 0x7fffffff || q.x > best) { best = q.x; idx = i; }
+            if (q.y > best) { best = q.y; idx = i + 1; }
+            if (q.z > best) { best = q.z; idx = i + 2; }
+            if (q.w > best) { best = q.w; idx = i + 3; }
+        };
+        int i = threadIdx.x;
+        for (; i + 3 * NT < n4; i += 4 * NT) {
+            const float4 a = row4[i], b = row4[i + NT], c = row4[i + 2 * NT], d = row4[i + 3 * NT];
+            take(a, 4 * i); take(b, 4 * (i + NT)); take(c, 4 * (i + 2 * NT)); take(d, 4 * (i + 3 * NT));
+        }
+        for (; i < n4; i += NT) take(row4[i], 4 * i);
+        done = n4 << 2;
+    }
+    for (int i = done + threadIdx.x; i < V; i += NT) {
+        const float v = row[i];
+        if (idx == 0x7fffffff || better(v, i, best, idx)) { best = v; idx = i; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -50,6 +70,87 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float* __restrict__ lo
             if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
         }
         if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+// The same over several CTAs per row: a row of 150,000 logits read by one SM takes as long as a small product, because
+// one SM has only so many bytes under way.  CTA (row, part) finds the best of its part of the row; the CTA that
+// arrives last at the row's counter (no waiting: the others have left by then) picks among the parts in ascending
+// order, so that a tie still goes to the lowest id, and puts the counter back to zero for the next call.
+constexpr int PARTS_THREADS = 256;
+constexpr int MAX_PARTS = 64;
+
+__global__ void __launch_bounds__(PARTS_THREADS)
+argmax_parts_kernel(const float* __restrict__ logits, int V, int per_part, int32_t* __restrict__ out, int* __restrict__ counters,
+                    float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float bv[PARTS_THREADS / 32];
+    __shared__ int bi[PARTS_THREADS / 32];
+    __shared__ int last;
+    const int r = blockIdx.x, c = blockIdx.y, parts = gridDim.y;
+    const float* row = logits + (size_t)r * V;
+    const int lo = c * per_part, hi = min(V, lo + per_part);
+    auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    int done = lo;
+    if ((((uintptr_t)(row + lo)) & 15) == 0 && hi > lo) {
+        const float4* p4 = (const float4*)(row + lo);
+        const int n4 = (hi - lo) >> 2;
+        auto take = [&](const float4& q, int i) {                      // ids ascend inside a vector: a tie keeps the lower id
+            const int id = lo + 4 * i;
+            if (idx == 0x7fffffff || q.x > best) { best = q.x; idx = id; }
+            if (q.y > best) { best = q.y; idx = id + 1; }
+            if (q.z > best) { best = q.z; idx = id + 2; }
+            if (q.w > best) { best = q.w; idx = id + 3; }
+        };
+        int i = threadIdx.x;
+        for (; i + 3 * PARTS_THREADS < n4; i += 4 * PARTS_THREADS) {    // four loads under way per thread
+            const float4 a = p4[i], b = p4[i + PARTS_THREADS], c4 = p4[i + 2 * PARTS_THREADS], d = p4[i + 3 * PARTS_THREADS];
+            take(a, i); take(b, i + PARTS_THREADS); take(c4, i + 2 * PARTS_THREADS); take(d, i + 3 * PARTS_THREADS);
+        }
+        for (; i < n4; i += PARTS_THREADS) take(p4[i], i);
+        done = lo + (n4 << 2);
+    }
+    for (int i = done + threadIdx.x; i < hi; i += PARTS_THREADS) {
+        const float v = row[i];
+        if (idx == 0x7fffffff || better(v, i, best, idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < PARTS_THREADS / 32; ++w)
+            if (better(bv[w], bi[w], best, idx)) { best = bv[w]; idx = bi[w]; }
+        part_val[(size_t)r * parts + c] = best;
+        part_idx[(size_t)r * parts + c] = idx;
+        __threadfence();                                            // the part is visible before the arrival is
+        last = atomicAdd(&counters[r], 1) == parts - 1;
+    }
+    __syncthreads();
+    if (!last || warp != 0) return;
+    __threadfence();
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int k = lane; k < parts; k += 32) {
+        const float v = __ldcg(&part_val[(size_t)r * parts + k]);
+        const int i = __ldcg(&part_idx[(size_t)r * parts + k]);
+        if (better(v, i, best, idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    if (lane == 0) {
+        out[r] = idx == 0x7fffffff ? 0 : idx;
+        counters[r] = 0;
     }
 }
 
@@ -419,6 +520,30 @@ __global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restric
 }
 
 }  // namespace
+
+// scratch: device memory of at least ph_argmax_scratch_bytes(R) bytes whose first 4 * R bytes are zero before the first
+// call (the kernel leaves them zero); calls that share a scratch must not overlap.
+PH_EXPORT long long ph_argmax_scratch_bytes(int R) { return (long long)R * (4 + (long long)MAX_PARTS * 8); }
+
+PH_EXPORT int ph_argmax_parts(const float* logits, int R, int V, int32_t* out, void* scratch, long long scratch_bytes,
+                              cudaStream_t stream) {
+    if (!logits || !out || R < 0 || V < 1) return fail(PH_ERR_ARG, "argmax: bad arguments (rows %d, V %d)", R, V);
+    if (R == 0) return PH_OK;
+    // parts of about 4,096 values, as many as fill the device once, a multiple of four values each
+    int parts = (2 * 148 + R - 1) / R;
+    parts = parts < 1 ? 1 : (parts > MAX_PARTS ? MAX_PARTS : parts);
+    if (parts > (V + 4095) / 4096) parts = (V + 4095) / 4096;
+    if (parts <= 1 || !scratch || scratch_bytes < ph_argmax_scratch_bytes(R) || R > 65535) {
+        argmax_kernel<<<R, NT, 0, stream>>>(logits, V, out);
+        return check_launch("argmax");
+    }
+    const int per_part = (((V + parts - 1) / parts) + 3) & ~3;
+    int* counters = (int*)scratch;
+    float* part_val = (float*)(counters + R);
+    int* part_idx = (int*)(part_val + (size_t)R * MAX_PARTS);
+    argmax_parts_kernel<<<dim3(R, parts), PARTS_THREADS, 0, stream>>>(logits, V, per_part, out, counters, part_val, part_idx);
+    return check_launch("argmax");
+}
 
 PH_EXPORT int ph_argmax(const float* logits, int R, int V, int32_t* out, cudaStream_t stream) {
     if (!logits || !out || R < 0 || V < 1) return fail(PH_ERR_ARG, "argmax: bad arguments (rows %d, V %d)", R, V);

@@ -453,12 +453,15 @@ PendingTokens* Engine::sample_async(const Tensor& logits, const std::vector<Samp
         slot.host.ensure((size_t)(slot.capacity + 2) * 4);
         slot.params.ensure((size_t)slot.capacity * 24);
         slot.ids = DeviceBuffer((size_t)slot.capacity * 4);
+        // the greedy kernel's scratch (partial results of the CTAs that share a row; its counters start at zero)
+        slot.scratch = DeviceBuffer((size_t)core_kernels().argmax_scratch_bytes(slot.capacity));
+        QE_CUDA(cudaMemsetAsync(slot.scratch.data(), 0, slot.scratch.bytes(), stream_));
     }
     const CoreKernels& k = core_kernels();
     const int V = (int)logits.shape[1];
     int32_t* ids = static_cast<int32_t*>(slot.ids.data());
     if (mode == Sampler::DeviceMode::Greedy) {
-        QE_LAUNCH(k, k.argmax(logits.as<float>(), R, V, ids, stream_));
+        QE_LAUNCH(k, k.argmax(logits.as<float>(), R, V, ids, slot.scratch.data(), (long long)slot.scratch.bytes(), stream_));
     } else if (mode == Sampler::DeviceMode::Chain) {
         ChainRecord* rec = static_cast<ChainRecord*>(slot.params.data());
         for (int i = 0; i < R; i++) rec[i] = samplers[i]->chain_record();

@@ -184,7 +184,7 @@ private:
     // graphs of single-token batches, most recently used last
     std::list<std::pair<std::string, std::unique_ptr<Graph>>> graphs_;
     // sampling
-    struct PendingSlot { PendingTokens p; int capacity = 0; PinnedBuffer host, params; DeviceBuffer ids; };
+    struct PendingSlot { PendingTokens p; int capacity = 0; PinnedBuffer host, params; DeviceBuffer ids, scratch; };
     PendingSlot pending_[4];
     int pending_turn_ = 0;
     std::function<void(int, const float*, int, int)> layer_dump_;

@@ -150,7 +150,8 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_add_weight_sumsq", g_core.add_weight_sumsq);
     bind(h, "core", "ph_attention_generic", g_core.attention_generic);
     bind(h, "core", "ph_gemm_simple", g_core.gemm_simple);
-    bind(h, "core", "ph_argmax", g_core.argmax);
+    bind(h, "core", "ph_argmax_parts", g_core.argmax);
+    bind(h, "core", "ph_argmax_scratch_bytes", g_core.argmax_scratch_bytes);
     bind(h, "core", "ph_sample_temperature", g_core.sample_temperature);
     bind(h, "core", "ph_sample_chain", g_core.sample_chain);
     bind(h, "core", "ph_sample_chain_max_k", g_core.sample_chain_max_k);

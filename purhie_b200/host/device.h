@@ -100,7 +100,8 @@ struct CoreKernels {
     int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
                              const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, cudaStream_t);
     int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
-    int (*argmax)(const float*, int, int, int32_t*, cudaStream_t);
+    int (*argmax)(const float*, int, int, int32_t*, void*, long long, cudaStream_t);   // several CTAs per row, with scratch
+    long long (*argmax_scratch_bytes)(int);
     int (*sample_temperature)(const float*, int, int, const float*, const double*, float, int32_t*, cudaStream_t);
     int (*sample_chain)(const float*, int, int, const void*, int32_t*, cudaStream_t);
     int (*sample_chain_max_k)(void);

@@ -416,6 +416,34 @@ def test_argmax_lowest_id_wins_ties():
     ops.argmax(l, out)
     ref = [int(torch.nonzero(r == r.max())[0]) for r in l]
     assert out.tolist() == ref and ref[:3] == [777, 151936, 0]
+    # rows that start on a 16-byte boundary are read four values at a time: ties inside one vector, across vectors
+    # that different threads read, in the last place, a row of equal values and a row of -inf
+    l = rnd(8, 151936, seed=9)
+    l[0, 4097] = l[0, 4098] = l[0, 90001] = 50.0
+    l[1, 151935] = 60.0
+    l[2, 3] = l[2, 4 * 1024 * 5 + 3] = 70.0
+    l[3, :] = 1.25
+    l[4, :] = float("-inf")
+    l[5, 151932] = l[5, 151933] = 80.0
+    out = torch.empty(8, dtype=torch.int32, device=DEV)
+    ops.argmax(l, out)
+    ref = [int(torch.nonzero(r == r.max())[0]) for r in l]
+    assert out.tolist() == ref and ref[:6] == [4097, 151935, 3, 0, 0, 151932]
+    # several CTAs per row (the form the engine runs): the same choices, call after call on the same scratch, for
+    # one row, for rows that do not start on a 16-byte boundary and for more rows than fill the device
+    for rows, V in ((8, 151936), (1, 151936), (6, 151937), (300, 5000), (3, 100)):
+        m = rnd(rows, V, seed=10 + rows)
+        if V > 4200:
+            m[0, 4095] = m[0, 4096] = m[0, V - 1] = 90.0                   # a tie across the boundary of two parts
+        if rows == 8:
+            m = l
+        scratch = torch.zeros(rows * (4 + 64 * 8), dtype=torch.uint8, device=DEV)
+        want = [int(torch.nonzero(r == r.max())[0]) for r in m]
+        for _ in range(3):
+            got = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+            ops.argmax(m, got, scratch=scratch)
+            assert got.tolist() == want, (rows, V)
+        assert int(scratch[:4 * rows].view(torch.int32).abs().sum()) == 0     # the counters are back at zero
 
 
 def test_sample_temperature_follows_the_distribution_and_the_host_chain():
