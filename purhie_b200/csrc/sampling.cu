@@ -521,8 +521,9 @@ __global__ void __launch_bounds__(NT) sample_chain_kernel(const float* __restric
 
 }  // namespace
 
-// scratch: device memory of at least ph_argmax_scratch_bytes(R) bytes whose first 4 * R bytes are zero before the first
-// call (the kernel leaves them zero); calls that share a scratch must not overlap.
+// scratch: device memory of at least ph_argmax_scratch_bytes(R) bytes, zero before the first call (the kernel leaves
+// its counters, the first 4 bytes per row the scratch has room for, at zero); calls that share a scratch must not
+// overlap and must give its size the same way.
 PH_EXPORT long long ph_argmax_scratch_bytes(int R) { return (long long)R * (4 + (long long)MAX_PARTS * 8); }
 
 PH_EXPORT int ph_argmax_parts(const float* logits, int R, int V, int32_t* out, void* scratch, long long scratch_bytes,
@@ -538,9 +539,11 @@ PH_EXPORT int ph_argmax_parts(const float* logits, int R, int V, int32_t* out, v
         return check_launch("argmax");
     }
     const int per_part = (((V + parts - 1) / parts) + 3) & ~3;
+    // the counters keep their place whatever the number of rows of a call: they must be found at zero by the next one
+    const long long rows_cap = scratch_bytes / (4 + (long long)MAX_PARTS * 8);
     int* counters = (int*)scratch;
-    float* part_val = (float*)(counters + R);
-    int* part_idx = (int*)(part_val + (size_t)R * MAX_PARTS);
+    float* part_val = (float*)(counters + rows_cap);
+    int* part_idx = (int*)(part_val + (size_t)rows_cap * MAX_PARTS);
     argmax_parts_kernel<<<dim3(R, parts), PARTS_THREADS, 0, stream>>>(logits, V, per_part, out, counters, part_val, part_idx);
     return check_launch("argmax");
 }

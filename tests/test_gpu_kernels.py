@@ -444,6 +444,13 @@ def test_argmax_lowest_id_wins_ties():
             ops.argmax(m, got, scratch=scratch)
             assert got.tolist() == want, (rows, V)
         assert int(scratch[:4 * rows].view(torch.int32).abs().sum()) == 0     # the counters are back at zero
+    # one scratch for calls of changing numbers of rows, as a server's steps have them
+    scratch = torch.zeros(64 * (4 + 64 * 8), dtype=torch.uint8, device=DEV)
+    for rows in (24, 3, 64, 10, 24, 1, 17):
+        m = rnd(rows, 151936, seed=40 + rows)
+        got = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        ops.argmax(m, got, scratch=scratch)
+        assert got.tolist() == m.argmax(-1).tolist(), rows
 
 
 def test_sample_temperature_follows_the_distribution_and_the_host_chain():

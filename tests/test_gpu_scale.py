@@ -293,6 +293,23 @@ def test_a_sliding_window_layer_at_real_layer_sizes():
         assert rel(b16[name], f32[name]) < 3e-2, name
 
 
+def test_greedy_generation_through_the_queue_does_not_depend_on_who_else_decodes():
+    """Five prompts of 30 to 2,000 tokens through the request queue in float32 at the 8B-class layer shape: their
+    prompts come in portions, so the number of rows the greedy kernel picks for changes from step to step (it shares
+    one scratch between those calls).  Every request gets the tokens it gets when it runs alone."""
+    from purhie_b200.api import load_model_random
+    from purhie_b200.config import Qwen3Config
+    cfg = Qwen3Config.from_dict(SHAPES["8b"])
+    model = load_model_random(cfg, 7, "float32")
+    model.kv_cache_init(4096, max_sequences=6, page_size=16, kv_tokens=6 * 2200)
+    prompts = [ids(n, 950 + i) for i, n in enumerate((30, 700, 1300, 90, 2000))]
+    together = model.generate(prompts, max_new_tokens=12)
+    alone = [model.generate([p], max_new_tokens=12)[0] for p in prompts]
+    assert together == alone
+    assert all(len(t) == 12 and all(0 <= x < 32000 for x in t) for t in together)
+    model.free()
+
+
 def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
     """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
     8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
