@@ -310,6 +310,61 @@ def test_greedy_generation_through_the_queue_does_not_depend_on_who_else_decodes
     model.free()
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_drawn_schedules_at_real_layer_sizes(seed):
+    """Forty drawn steps at the 8B-class layer shape: up to four live requests, portions of 1 to 900 tokens beside
+    decode rows, requests that sit a step out, pages poisoned when freed and few enough to be used again.  Every
+    wanted row of the bfloat16 engine lies within 3e-2 of the float32 engine's (by the row's largest logit)."""
+    from purhie_b200.engine import Engine, StepEntry
+    rng = np.random.default_rng(seed)
+    reqs, steps, next_id = {}, [], 0
+    for _ in range(40):
+        entries, end = [], []
+        live = [r for r in reqs if reqs[r]["fed"] < len(reqs[r]["toks"])]
+        while len(live) < 4 and rng.random() < 0.6:
+            n = int(rng.choice([5, 40, 300, 900, 1700]))
+            reqs[next_id] = {"toks": rng.integers(0, 32000, n + int(rng.integers(1, 12))).tolist(), "fed": 0, "prompt": n}
+            live.append(next_id)
+            next_id += 1
+        for r in live:
+            if rng.random() < 0.25:
+                continue
+            q = reqs[r]
+            left = q["prompt"] - q["fed"]
+            n = int(min(left, rng.choice([1, 2, 7, 64, 128, 129, 300, 513, 900]))) if left > 0 else 1
+            want = sorted(set(int(x) for x in rng.integers(0, n, min(n, 3)))) if rng.random() < 0.8 else []
+            entries.append((r, q["toks"][q["fed"]:q["fed"] + n], want))
+            q["fed"] += n
+            if q["fed"] >= len(q["toks"]):
+                end.append(r)
+        if entries:
+            steps.append((entries, end))
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(SHAPES["8b"], 7, dtype=dtype, page_size=16, max_tokens=4 * 1800, max_requests=4, poison_cache=True)
+        known, res = set(), []
+        for entries, end in steps:
+            for r, _, _ in entries:
+                if r not in known:
+                    eng.add_request(r)
+                    known.add(r)
+            lg = eng.step([StepEntry(r, t, w) for r, t, w in entries])
+            res.append(None if lg is None or len(lg) == 0 else np.asarray(lg))
+            for r in end:
+                eng.release(r)
+        out[dtype] = res
+        eng.close()
+    rows = 0
+    for i, (a, b) in enumerate(zip(out["bfloat16"], out["float32"])):
+        if b is None:
+            continue
+        assert not np.isnan(b).any() and not np.isnan(a).any(), i
+        err = np.abs(a - b).max(axis=1) / np.abs(b).max(axis=1)
+        assert err.max() < 3e-2, (i, float(err.max()))
+        rows += len(err)
+    assert rows > 80
+
+
 def test_batch_64_decoding_as_graphs_at_real_layer_sizes():
     """64 requests of 30 to 1,500 tokens decode six steps side by side (graph replays from the second step on) at the
     8B-class layer shape: bfloat16 stays as close to the float32 engine as it is for single requests."""
